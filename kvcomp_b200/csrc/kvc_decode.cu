@@ -1,0 +1,105 @@
+// Blocked Huffman decoder to uint8 codes (kernels.cu:602-719 restated for sm_100a).
+//
+// CTA = 256 threads = 4 blocks of 64 vectors per round, grid-stride over block groups so that the
+// decode table is brought into shared memory once per CTA.  Thread = one vector; decoded symbols
+// go to a shared-memory tile and leave as coalesced 32-bit stores (K: rows, V: transposed back).
+#include "kvc_decode.cuh"
+
+namespace {
+
+constexpr int SLOT_BYTES = 8192 + 32;      // a block is at most 8191 bytes (u16 fields) + alignment lead
+constexpr int TILE_STRIDE = 132;
+
+struct DecodeSmem {
+    KvcBookSmem book;
+    uint8_t slot[4][SLOT_BYTES];
+    uint8_t tile[4][64 * TILE_STRIDE];
+};
+
+__global__ void __launch_bounds__(256) decode_kernel(
+    const uint8_t *__restrict__ encoded, long long encoded_bytes, const uint2 *__restrict__ block_info,
+    const uint16_t *__restrict__ thread_info, const void *__restrict__ book, long long nblk, long long cols, int is_k,
+    uint8_t *__restrict__ codes, int *__restrict__ status) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    DecodeSmem &sm = *reinterpret_cast<DecodeSmem *>(smem_raw);
+    const int tid = threadIdx.x, sub = tid >> 6, v = tid & 63;      // sub-block and vector of this thread
+    const long long row = cols * 128;
+    kvc_load_book(sm.book, book, tid, 256);
+    int flags = 0;
+    for (long long grp = blockIdx.x; grp * 4 < nblk; grp += gridDim.x) {
+        const long long blk = grp * 4 + sub;
+        const bool active = blk < nblk;
+        uint32_t lead = 0, nbytes = 0;
+        __syncthreads();                       // previous round's tile and slot are free (and the book is in)
+        if (active) {
+            const uint2 bi = block_info[blk];
+            nbytes = bi.y & 0xffffu;
+            if (nbytes > 8191u || (long long)bi.x + nbytes > encoded_bytes) { nbytes = 0; flags |= KVC_FLAG_BAD_STREAM; }
+            lead = kvc_stage_block(sm.slot[sub], encoded, encoded_bytes, bi.x, nbytes, v, 64);
+        }
+        __syncthreads();
+        if (active && nbytes) {
+            const uint32_t start = v ? (uint32_t)(thread_info[blk * 64 + v - 1] >> 3) : 0u;
+            uint8_t *trow = sm.tile[sub] + v * TILE_STRIDE;
+            bool ok = start < nbytes;
+            if (ok)
+                ok = kvc_decode_vector(reinterpret_cast<const uint32_t *>(sm.slot[sub]), lead + start, SLOT_BYTES / 4 - 1, sm.book,
+                                       [&](uint32_t s0, uint32_t s1, uint32_t s2, uint32_t ns, int c) {
+                                           if (c < 128) trow[c] = (uint8_t)s0;
+                                           if (ns > 1 && c + 1 < 128) trow[c + 1] = (uint8_t)s1;
+                                           if (ns > 2 && c + 2 < 128) trow[c + 2] = (uint8_t)s2;
+                                       });
+            if (!ok) flags |= KVC_FLAG_BAD_STREAM;
+        }
+        __syncthreads();
+        if (active && nbytes) {
+            const uint8_t *tile = sm.tile[sub];
+            if (is_k) {
+                const long long j = blk / cols, col = blk % cols;
+                uint8_t *dst = codes + (j * 64) * row + col * 128;
+                for (int i = v; i < 64 * 32; i += 64) {
+                    int r = i >> 5, w = i & 31;
+                    *reinterpret_cast<uint32_t *>(dst + r * row + w * 4) =
+                        *reinterpret_cast<const uint32_t *>(tile + r * TILE_STRIDE + w * 4);
+                }
+            } else {
+                const long long g = blk / (cols * 2), m = blk % (cols * 2);
+                uint8_t *dst = codes + (g * 128) * row + m * 64;
+                for (int i = v; i < 128 * 16; i += 64) {
+                    int t = i >> 4, w = i & 15;
+                    uint32_t x = 0;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) x |= (uint32_t)tile[(w * 4 + k) * TILE_STRIDE + t] << (8 * k);
+                    *reinterpret_cast<uint32_t *>(dst + t * row + w * 4) = x;
+                }
+            }
+        }
+    }
+    if (flags) atomicOr(status, flags);
+}
+
+}  // namespace
+
+extern "C" int kvc_decode(const uint8_t *encoded, int64_t encoded_bytes, const void *block_info,
+                          const uint16_t *thread_info, const void *book, int64_t T, int64_t cols, int is_k,
+                          uint8_t *codes, int32_t *status, kvc_stream_t stream) {
+    KVC_REQUIRE(encoded && block_info && thread_info && book && codes && status, "kvc_decode: null pointer");
+    KVC_REQUIRE(cols > 0 && T >= 0 && encoded_bytes >= 0, "kvc_decode: bad shape");
+    KVC_REQUIRE(T % (is_k ? 64 : 128) == 0, "kvc_decode: %s needs a multiple of %d tokens, got %lld",
+                is_k ? "K" : "V", is_k ? 64 : 128, (long long)T);
+    KVC_REQUIRE((reinterpret_cast<uintptr_t>(codes) & 3) == 0 && (reinterpret_cast<uintptr_t>(block_info) & 7) == 0 &&
+                (reinterpret_cast<uintptr_t>(book) & 15) == 0, "kvc_decode: misaligned pointer");
+    const long long nblk = is_k ? (T / 64) * cols : (T / 128) * cols * 2;
+    if (nblk == 0) return KVC_OK;
+    static bool attr_set = false;
+    if (!attr_set) {
+        KVC_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecodeSmem)));
+        attr_set = true;
+    }
+    long long groups = (nblk + 3) / 4, cap = (long long)kvc_sm_count() * 3;
+    unsigned grid = (unsigned)(groups < cap ? groups : cap);
+    decode_kernel<<<grid, 256, sizeof(DecodeSmem), kvc_cu(stream)>>>(
+        encoded, encoded_bytes, reinterpret_cast<const uint2 *>(block_info), thread_info, book, nblk, cols, is_k, codes, status);
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}

@@ -1,0 +1,269 @@
+// Blocked Huffman encoder (kernels.cu:181-235, 419-596 restated for sm_100a).
+//
+// Three phases, no inter-CTA waiting and a deterministic stream:
+//   A  sizes   one CTA per block: stage the 64x128 code tile in shared memory, a warp per
+//              vector sums code lengths with shuffles -> thread_info, block byte count
+//   B  scan    exclusive prefix sum of block byte counts -> block_info offsets (ascending id)
+//   C  emit    one CTA per block: each lane places its 4 codes at their bit offsets (warp-shuffle
+//              prefix sum of lengths) into a shared-memory image of the block that is aligned
+//              like its destination, then the image goes out as 128-bit stores
+#include "kvc_common.cuh"
+
+namespace {
+
+constexpr int TILE_STRIDE = 132;                  // bytes per vector row in shared memory (padded)
+constexpr int OUT_CAP = 8192 + 32;                // block image: 8191 bytes max + alignment lead + slack
+
+struct EncTable { uint32_t code[256]; uint32_t len[256]; };
+
+__device__ __forceinline__ void load_table(EncTable &t, const uint32_t *__restrict__ enc, int n_entries, int tid, int nthr) {
+    for (int i = tid; i < 256; i += nthr) {
+        bool ok = i < n_entries;
+        t.code[i] = ok ? enc[2 * i] : 0u;
+        t.len[i] = ok ? enc[2 * i + 1] : 0u;
+    }
+}
+
+// Stage the code tile of block `blk` as tile[vector][symbol].
+// K: vector v = token 64j+v, symbols = its 128 channels (rows of 128 contiguous bytes).
+// V: vector v = channel column 64m+v, symbols = tokens 128g..128g+127 (transposed on the way in).
+__device__ __forceinline__ void stage_tile(uint8_t *tile, const uint8_t *__restrict__ codes, long long blk,
+                                           long long cols, int is_k, int tid) {
+    const long long row = cols * 128;
+    if (is_k) {
+        const long long j = blk / cols, col = blk % cols;
+        const uint8_t *src = codes + (j * 64) * row + col * 128;
+        for (int i = tid; i < 64 * 32; i += 256) {             // 64 rows x 32 words
+            int v = i >> 5, w = i & 31;
+            uint32_t x = *reinterpret_cast<const uint32_t *>(src + v * row + w * 4);
+            *reinterpret_cast<uint32_t *>(tile + v * TILE_STRIDE + w * 4) = x;
+        }
+    } else {
+        const long long g = blk / (cols * 2), m = blk % (cols * 2);
+        const uint8_t *src = codes + (g * 128) * row + m * 64;
+        for (int i = tid; i < 128 * 16; i += 256) {            // 128 token rows x 16 words
+            int t = i >> 4, w = i & 15;
+            uint32_t x = *reinterpret_cast<const uint32_t *>(src + t * row + w * 4);
+#pragma unroll
+            for (int k = 0; k < 4; k++) tile[(w * 4 + k) * TILE_STRIDE + t] = (uint8_t)(x >> (8 * k));
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t warp_excl_scan(uint32_t v, int lane, uint32_t *total) {
+    uint32_t x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { uint32_t y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+    *total = __shfl_sync(0xffffffffu, x, 31);
+    return x - v;
+}
+
+// ---- phase A ----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) encode_sizes_kernel(
+    const uint8_t *__restrict__ codes, long long cols, int is_k, const uint32_t *__restrict__ enc, int n_entries,
+    uint16_t *__restrict__ thread_info, uint32_t *__restrict__ sizes, unsigned long long *__restrict__ partial,
+    int *__restrict__ status) {
+    __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE];
+    __shared__ EncTable tab;
+    __shared__ uint32_t vbits[64];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long blk = blockIdx.x;
+    load_table(tab, enc, n_entries, tid, 256);
+    stage_tile(tile, codes, blk, cols, is_k, tid);
+    __syncthreads();
+    int flags = 0;
+    for (int v = warp; v < 64; v += 8) {
+        uint32_t x = *reinterpret_cast<const uint32_t *>(tile + v * TILE_STRIDE + lane * 4);
+        uint32_t bits = 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            uint32_t l = tab.len[(x >> (8 * k)) & 0xffu];
+            if (l == 0) flags |= KVC_FLAG_SYMBOL_MISSING;
+            bits += l;
+        }
+        bits = (uint32_t)__reduce_add_sync(0xffffffffu, bits);
+        if (lane == 0) vbits[v] = bits;
+    }
+    __syncthreads();
+    if (warp == 0) {       // byte offsets of the 64 vectors: two per lane
+        uint32_t b0 = vbits[2 * lane], b1 = vbits[2 * lane + 1];
+        uint32_t n0 = (b0 + 7) >> 3, n1 = (b1 + 7) >> 3, total;
+        uint32_t start = warp_excl_scan(n0 + n1, lane, &total);
+        uint32_t e0 = start + n0, e1 = e0 + n1;
+        if (n0 > (is_k ? 128u : 256u) || n1 > (is_k ? 128u : 256u)) flags |= KVC_FLAG_VECTOR_LONG;
+        // kernels.cu:462-465: (end byte << 3) + pad bits
+        thread_info[blk * 64 + 2 * lane] = (uint16_t)((e0 << 3) + (n0 * 8 - b0));
+        thread_info[blk * 64 + 2 * lane + 1] = (uint16_t)((e1 << 3) + (n1 * 8 - b1));
+        if (lane == 0) {
+            sizes[blk] = total;
+            atomicAdd(&partial[blk >> 10], (unsigned long long)total);
+            if (total > 8191u) flags |= KVC_FLAG_BLOCK_LONG;
+        }
+    }
+    if (flags) atomicOr(status, flags);
+}
+
+// ---- phase B ----------------------------------------------------------------------------------
+// partial[i] = byte count of blocks [1024 i, 1024 i + 1024); turn it into an exclusive prefix and
+// leave the grand total in partial[n_part].
+__global__ void __launch_bounds__(1024) scan_partials_kernel(unsigned long long *__restrict__ partial, long long n_part,
+                                                             unsigned long long *__restrict__ total_out) {
+    __shared__ unsigned long long wsum[32];
+    __shared__ unsigned long long carry;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) carry = 0;
+    __syncthreads();
+    for (long long base = 0; base < n_part; base += 1024) {
+        long long i = base + tid;
+        unsigned long long v = i < n_part ? partial[i] : 0ull, x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { unsigned long long y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+        if (lane == 31) wsum[warp] = x;
+        __syncthreads();
+        if (warp == 0) {
+            unsigned long long w = wsum[lane], z = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { unsigned long long y = __shfl_up_sync(0xffffffffu, z, o); if (lane >= o) z += y; }
+            wsum[lane] = z - w;
+        }
+        __syncthreads();
+        unsigned long long excl = carry + wsum[warp] + x - v;
+        if (i < n_part) partial[i] = excl;
+        __syncthreads();
+        if (tid == 1023) carry = excl + v;
+        __syncthreads();
+    }
+    if (tid == 0) { partial[n_part] = carry; if (total_out) *total_out = carry; }
+}
+
+__global__ void __launch_bounds__(1024) scan_blocks_kernel(const uint32_t *__restrict__ sizes, long long nblk,
+                                                           const unsigned long long *__restrict__ partial,
+                                                           uint32_t base_offset, long long capacity,
+                                                           uint2 *__restrict__ block_info, int *__restrict__ status) {
+    __shared__ uint32_t wsum[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long i = (long long)blockIdx.x * 1024 + tid;
+    uint32_t v = i < nblk ? sizes[i] : 0u, total;
+    uint32_t x = warp_excl_scan(v, lane, &total);
+    if (lane == 31) wsum[warp] = total;
+    __syncthreads();
+    if (warp == 0) { uint32_t w = wsum[lane], t2; uint32_t z = warp_excl_scan(w, lane, &t2); wsum[lane] = z; }
+    __syncthreads();
+    if (i < nblk) {
+        unsigned long long off = partial[blockIdx.x] + wsum[warp] + x;
+        int flags = 0;
+        if ((long long)(off + v) > capacity) flags |= KVC_FLAG_STREAM_FULL;
+        if (off + v + base_offset > 0xffffffffull) flags |= KVC_FLAG_STREAM_FULL;     // u32 offsets
+        block_info[i] = make_uint2((uint32_t)(off + base_offset), v & 0xffffu);      // {u32, u16, 2 B zero}
+        if (flags) atomicOr(status, flags);
+    }
+}
+
+// ---- phase C ----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) encode_emit_kernel(
+    const uint8_t *__restrict__ codes, long long cols, int is_k, const uint32_t *__restrict__ enc, int n_entries,
+    const uint16_t *__restrict__ thread_info, const uint2 *__restrict__ block_info,
+    const uint32_t *__restrict__ sizes, uint32_t base_offset, uint8_t *__restrict__ encoded, long long capacity) {
+    __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE];
+    __shared__ __align__(16) uint32_t out[OUT_CAP / 4];
+    __shared__ EncTable tab;
+    __shared__ uint16_t tinfo[64];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long blk = blockIdx.x;
+    const uint2 bi = block_info[blk];
+    const long long off = (long long)bi.x - base_offset;
+    const uint32_t nbytes = sizes[blk];
+    // an oversized block cannot be described by its u16 fields; a full stream has no room: skip
+    if (nbytes > 8191u || off + nbytes > capacity) return;
+    load_table(tab, enc, n_entries, tid, 256);
+    stage_tile(tile, codes, blk, cols, is_k, tid);
+    if (tid < 64) tinfo[tid] = thread_info[blk * 64 + tid];
+    for (int i = tid; i < OUT_CAP / 4; i += 256) out[i] = 0;
+    __syncthreads();
+    uint8_t *dst = encoded + off;
+    const uint32_t lead = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15);   // image is aligned like dst
+    for (int v = warp; v < 64; v += 8) {
+        uint32_t x = *reinterpret_cast<const uint32_t *>(tile + v * TILE_STRIDE + lane * 4);
+        uint32_t c[4], l[4], bits = 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            uint32_t s = (x >> (8 * k)) & 0xffu;
+            c[k] = tab.code[s]; l[k] = tab.len[s]; bits += l[k];
+        }
+        uint32_t total;
+        uint32_t p = warp_excl_scan(bits, lane, &total);
+        p += 8u * (lead + (v ? (uint32_t)(tinfo[v - 1] >> 3) : 0u));
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            if (l[k]) {
+                uint32_t w = p >> 5, s = p & 31u;
+                unsigned long long val = (unsigned long long)c[k] << (64 - l[k] - s);
+                atomicOr(&out[w], (uint32_t)(val >> 32));
+                if ((uint32_t)val) atomicOr(&out[w + 1], (uint32_t)val);
+                p += l[k];
+            }
+        }
+    }
+    __syncthreads();
+    // image words hold stream bytes most-significant first; swap to memory order on the way out
+    const uint32_t end = lead + nbytes;
+    uint8_t *g0 = dst - lead;                                   // 16-byte aligned
+    for (uint32_t ch = tid; ch * 16 < end; ch += 256) {
+        uint32_t b0 = ch * 16, b1 = b0 + 16;
+        uint4 wv = *reinterpret_cast<const uint4 *>(&out[ch * 4]);
+        wv.x = kvc_bswap(wv.x); wv.y = kvc_bswap(wv.y); wv.z = kvc_bswap(wv.z); wv.w = kvc_bswap(wv.w);
+        if (b0 >= lead && b1 <= end) {
+            *reinterpret_cast<uint4 *>(g0 + b0) = wv;
+        } else {                                                // shared with a neighbouring block
+            const uint8_t *bytes = reinterpret_cast<const uint8_t *>(&wv);
+            for (uint32_t b = (b0 < lead ? lead : b0); b < (b1 < end ? b1 : end); b++) g0[b] = bytes[b - b0];
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int64_t kvc_encode_workspace(int64_t T, int64_t cols, int is_k) {
+    int64_t nblk = is_k ? (T / 64) * cols : (T / 128) * cols * 2;
+    int64_t n_part = (nblk + 1023) / 1024;
+    return ((nblk * 4 + 15) / 16) * 16 + (n_part + 1) * 8;
+}
+
+extern "C" int kvc_encode(const uint8_t *codes, int64_t T, int64_t cols, int is_k,
+                          const void *enc_table, int n_entries, uint32_t base_offset,
+                          void *block_info, uint16_t *thread_info, uint8_t *encoded, int64_t encoded_capacity,
+                          unsigned long long *total_bytes, void *workspace, int64_t workspace_bytes,
+                          int32_t *status, kvc_stream_t stream) {
+    KVC_REQUIRE(codes && enc_table && block_info && thread_info && encoded && status, "kvc_encode: null pointer");
+    KVC_REQUIRE(cols > 0 && T >= 0, "kvc_encode: bad shape");
+    KVC_REQUIRE(n_entries >= 1 && n_entries <= 256, "kvc_encode: the encode table has 1..256 entries");
+    KVC_REQUIRE(T % (is_k ? 64 : 128) == 0, "kvc_encode: %s needs a multiple of %d tokens, got %lld",
+                is_k ? "K" : "V", is_k ? 64 : 128, (long long)T);
+    KVC_REQUIRE((reinterpret_cast<uintptr_t>(codes) & 3) == 0 && (reinterpret_cast<uintptr_t>(block_info) & 7) == 0,
+                "kvc_encode: codes must be 4-byte and block_info 8-byte aligned");
+    cudaStream_t s = kvc_cu(stream);
+    const long long nblk = is_k ? (T / 64) * cols : (T / 128) * cols * 2;
+    if (nblk == 0) {
+        if (total_bytes) KVC_CUDA_OK(cudaMemsetAsync(total_bytes, 0, 8, s));
+        return KVC_OK;
+    }
+    KVC_REQUIRE(nblk < (1ll << 31), "kvc_encode: too many blocks in one call");
+    KVC_REQUIRE(workspace && workspace_bytes >= kvc_encode_workspace(T, cols, is_k),
+                "kvc_encode: workspace needs %lld bytes", (long long)kvc_encode_workspace(T, cols, is_k));
+    KVC_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "kvc_encode: workspace must be 16-byte aligned");
+    const long long n_part = (nblk + 1023) / 1024;
+    uint32_t *sizes = reinterpret_cast<uint32_t *>(workspace);
+    unsigned long long *partial = reinterpret_cast<unsigned long long *>(
+        reinterpret_cast<uint8_t *>(workspace) + ((nblk * 4 + 15) / 16) * 16);
+    const uint32_t *enc = reinterpret_cast<const uint32_t *>(enc_table);
+    KVC_CUDA_OK(cudaMemsetAsync(partial, 0, (n_part + 1) * 8, s));
+    encode_sizes_kernel<<<(unsigned)nblk, 256, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info, sizes, partial, status);
+    scan_partials_kernel<<<1, 1024, 0, s>>>(partial, n_part, total_bytes);
+    scan_blocks_kernel<<<(unsigned)n_part, 1024, 0, s>>>(sizes, nblk, partial, base_offset, encoded_capacity,
+                                                        reinterpret_cast<uint2 *>(block_info), status);
+    encode_emit_kernel<<<(unsigned)nblk, 256, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info,
+                                                     reinterpret_cast<const uint2 *>(block_info), sizes, base_offset,
+                                                     encoded, encoded_capacity);
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}

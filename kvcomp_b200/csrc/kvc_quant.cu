@@ -1,0 +1,395 @@
+// Error-bounded quantiser, dequantiser and the dense q.k baseline.
+//
+// Follows utils/compute.py:93-106 (quant) as torch evaluates it on fp16 tensors: every
+// elementwise op widens to fp32, computes, and rounds to nearest-even back to fp16; the
+// Python scalar `rel` stays fp32.  Explicit round-to-nearest intrinsics are used so that no
+// contraction or fast-math rewrite can change a bit.
+#include "kvc_common.cuh"
+
+namespace {
+
+struct UnitParam { float sf; float mi; };   // scale as float, min_int as float
+
+__device__ __forceinline__ UnitParam unit_param(float mn, float mx, float rel, __half *scale_out, int *flags) {
+    __half range = __float2half_rn(__fsub_rn(mx, mn));
+    __half sc = __float2half_rn(__fmul_rn(__half2float(range), rel));
+    UnitParam p;
+    p.sf = __half2float(sc);
+    if (p.sf == 0.0f || p.sf != p.sf) { p.mi = 0.0f; *flags |= KVC_FLAG_ZERO_SCALE; }
+    else p.mi = rintf(__half2float(__float2half_rn(__fdiv_rn(mn, p.sf))));
+    *scale_out = sc;
+    return p;
+}
+
+__device__ __forceinline__ void store_min(void *min_int, int min_bytes, long long u, float mi, int *flags) {
+    int v = (int)mi;
+    if (min_bytes == 1) {
+        if (v < -128 || v > 127) *flags |= KVC_FLAG_MIN_OVERFLOW;
+        reinterpret_cast<int8_t *>(min_int)[u] = (int8_t)v;      // wraps like the reference's .to(int8)
+    } else {
+        if (v < -32768 || v > 32767) *flags |= KVC_FLAG_MIN_OVERFLOW;
+        reinterpret_cast<int16_t *>(min_int)[u] = (int16_t)v;
+    }
+}
+
+__device__ __forceinline__ uint32_t quant_one(__half x, const UnitParam &p, int *flags) {
+    if (p.sf == 0.0f || p.sf != p.sf) return 0u;
+    float q = rintf(__half2float(__float2half_rn(__fdiv_rn(__half2float(x), p.sf))));
+    float c = __half2float(__float2half_rn(__fsub_rn(q, p.mi)));
+    if (!(c >= 0.0f && c <= 255.0f)) { *flags |= KVC_FLAG_CODE_OVERFLOW; }
+    return (uint32_t)(int)c & 0xffu;
+}
+
+// quantise 8 halves held in a uint4 -> 8 code bytes in a uint2; optional smem histogram
+__device__ __forceinline__ uint2 quant_eight(const uint4 &v, const UnitParam *p, int pstride, int *flags,
+                                             unsigned int *hist) {
+    const __half *h = reinterpret_cast<const __half *>(&v);
+    uint32_t c[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        c[i] = quant_one(h[i], p[i * pstride], flags);
+        if (hist) atomicAdd(&hist[c[i]], 1u);
+    }
+    uint2 o;
+    o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+    o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+    return o;
+}
+
+__device__ __forceinline__ void hist_flush(unsigned int *sh, unsigned long long *gh, int tid, int nthr) {
+    __syncthreads();
+    for (int i = tid; i < 256; i += nthr)
+        if (sh[i]) atomicAdd(&gh[i], (unsigned long long)sh[i]);
+}
+
+__device__ __forceinline__ void minmax8(const uint4 &v, float &mn, float &mx) {
+    const __half *h = reinterpret_cast<const __half *>(&v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) { float f = __half2float(h[i]); mn = fminf(mn, f); mx = fmaxf(mx, f); }
+}
+
+// ---- ChannelQuant (utils/compute.py:140): one unit per (token block, b, h, channel) -------------
+// CTA = one (j, b, h) tile of blk tokens x 128 channels; thread = 8 channels x every 8th token.
+__global__ void __launch_bounds__(128) quant_channel_kernel(
+    const __half *__restrict__ x, long long B, long long H, int blk, float rel,
+    uint8_t *__restrict__ codes, void *__restrict__ min_int, int min_bytes, __half *__restrict__ scale,
+    unsigned long long *__restrict__ ghist, int *__restrict__ status) {
+    __shared__ float smn[8][128], smx[8][128];
+    __shared__ unsigned int shist[256];
+    const int tid = threadIdx.x, cg = tid & 15, r = tid >> 4;
+    const long long tile = blockIdx.x;                 // (j * B + b) * H + h
+    const long long h = tile % H, b = (tile / H) % B, j = tile / (H * B);
+    const long long row_stride = B * H * 128;
+    const long long base = ((j * blk) * B + b) * H * 128 + h * 128 + cg * 8;
+    if (ghist) { for (int i = tid; i < 256; i += 128) shist[i] = 0; }
+    float mn[8], mx[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { mn[i] = INFINITY; mx[i] = -INFINITY; }
+    for (int i = r; i < blk; i += 8) {
+        uint4 v = *reinterpret_cast<const uint4 *>(x + base + i * row_stride);
+        const __half *hv = reinterpret_cast<const __half *>(&v);
+#pragma unroll
+        for (int k = 0; k < 8; k++) { float f = __half2float(hv[k]); mn[k] = fminf(mn[k], f); mx[k] = fmaxf(mx[k], f); }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; k++) { smn[r][cg * 8 + k] = mn[k]; smx[r][cg * 8 + k] = mx[k]; }
+    __syncthreads();
+    int flags = 0;
+    UnitParam p[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        float a = smn[0][cg * 8 + k], z = smx[0][cg * 8 + k];
+#pragma unroll
+        for (int rr = 1; rr < 8; rr++) { a = fminf(a, smn[rr][cg * 8 + k]); z = fmaxf(z, smx[rr][cg * 8 + k]); }
+        __half sc;
+        p[k] = unit_param(a, z, rel, &sc, &flags);
+        if (r == 0) {
+            long long u = tile * 128 + cg * 8 + k;
+            scale[u] = sc;
+            store_min(min_int, min_bytes, u, p[k].mi, &flags);
+        }
+    }
+    for (int i = r; i < blk; i += 8) {
+        uint4 v = *reinterpret_cast<const uint4 *>(x + base + i * row_stride);
+        uint2 o = quant_eight(v, p, 1, &flags, ghist ? shist : nullptr);
+        *reinterpret_cast<uint2 *>(codes + base + i * row_stride) = o;
+    }
+    if (flags) atomicOr(status, flags);
+    if (ghist) hist_flush(shist, ghist, tid, 128);
+}
+
+// ---- units that are contiguous runs of `ulen` elements -----------------------------------------
+// TokenQuant (all of a token's [B,]H,D values) and VectorQuant (one head's D values).
+// GROUP threads share one unit: a warp for short units, the whole CTA (256) for long ones.
+template <int GROUP>
+__global__ void __launch_bounds__(256) quant_contig_kernel(
+    const __half *__restrict__ x, long long n_units, long long ulen, float rel,
+    uint8_t *__restrict__ codes, void *__restrict__ min_int, int min_bytes, __half *__restrict__ scale,
+    unsigned long long *__restrict__ ghist, int *__restrict__ status) {
+    __shared__ float red[2][8];
+    __shared__ unsigned int shist[256];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int UNITS_PER_CTA = 256 / GROUP;
+    const long long u = (long long)blockIdx.x * UNITS_PER_CTA + (GROUP == 256 ? 0 : warp);
+    const int gl = GROUP == 256 ? tid : lane;          // index inside the group
+    if (ghist) { for (int i = tid; i < 256; i += 256) shist[i] = 0; __syncthreads(); }
+    const bool active = u < n_units;
+    const long long chunks = ulen / 8;
+    const __half *xu = x + u * ulen;
+    float mn = INFINITY, mx = -INFINITY;
+    if (active)
+        for (long long k = gl; k < chunks; k += GROUP) {
+            uint4 v = *reinterpret_cast<const uint4 *>(xu + k * 8);
+            minmax8(v, mn, mx);
+        }
+    mn = -kvc_warp_max(-mn); mx = kvc_warp_max(mx);
+    if (GROUP == 256) {
+        if (lane == 0) { red[0][warp] = mn; red[1][warp] = mx; }
+        __syncthreads();
+        mn = red[0][0]; mx = red[1][0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) { mn = fminf(mn, red[0][w]); mx = fmaxf(mx, red[1][w]); }
+    }
+    int flags = 0;
+    if (active) {
+        __half sc;
+        UnitParam p = unit_param(mn, mx, rel, &sc, &flags);
+        if (gl == 0) { scale[u] = sc; store_min(min_int, min_bytes, u, p.mi, &flags); }
+        for (long long k = gl; k < chunks; k += GROUP) {
+            uint4 v = *reinterpret_cast<const uint4 *>(xu + k * 8);
+            uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist : nullptr);
+            *reinterpret_cast<uint2 *>(codes + u * ulen + k * 8) = o;
+        }
+    }
+    if (flags) atomicOr(status, flags);
+    if (ghist) hist_flush(shist, ghist, tid, 256);
+}
+
+// ---- BlockQuant: one unit per token block (x sequence), far larger than a CTA ------------------
+// Three launches: per-row min/max folded into the unit with atomics on order-preserving keys,
+// a per-unit finalise, and the elementwise pass.  A row is one (token, b): H*D contiguous values.
+__device__ __forceinline__ unsigned int half_key(float f) {      // monotone in the value
+    unsigned int h = __half_as_ushort(__float2half_rn(f));
+    return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+}
+__device__ __forceinline__ float key_half(unsigned int k) {
+    unsigned int h = (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+__global__ void __launch_bounds__(256) quant_block_minmax_kernel(
+    const __half *__restrict__ x, long long B, long long row_len, int blk, int batch_shared,
+    unsigned int *__restrict__ ws) {
+    __shared__ float red[2][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long row = blockIdx.x, t = row / B, b = row % B;
+    const long long u = batch_shared ? t / blk : (t / blk) * B + b;
+    const __half *xr = x + row * row_len;
+    float mn = INFINITY, mx = -INFINITY;
+    for (long long k = tid; k < row_len / 8; k += 256) {
+        uint4 v = *reinterpret_cast<const uint4 *>(xr + k * 8);
+        minmax8(v, mn, mx);
+    }
+    mn = -kvc_warp_max(-mn); mx = kvc_warp_max(mx);
+    if (lane == 0) { red[0][warp] = mn; red[1][warp] = mx; }
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int w = 1; w < 8; w++) { mn = fminf(mn, red[0][w]); mx = fmaxf(mx, red[1][w]); }
+        atomicMax(&ws[2 * u], 0xffffu - half_key(mn));     // max of the inverted key == min of the value
+        atomicMax(&ws[2 * u + 1], half_key(mx));
+    }
+}
+
+__global__ void quant_block_finalize_kernel(unsigned int *__restrict__ ws, long long n_units, float rel,
+                                            void *__restrict__ min_int, int min_bytes,
+                                            __half *__restrict__ scale, int *__restrict__ status) {
+    long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= n_units) return;
+    float mn = key_half(0xffffu - ws[2 * u]), mx = key_half(ws[2 * u + 1]);
+    int flags = 0;
+    __half sc;
+    UnitParam p = unit_param(mn, mx, rel, &sc, &flags);
+    scale[u] = sc;
+    store_min(min_int, min_bytes, u, p.mi, &flags);
+    // leave the unit parameters where the elementwise pass reads them
+    ws[2 * u] = __float_as_uint(p.sf);
+    ws[2 * u + 1] = __float_as_uint(p.mi);
+    if (flags) atomicOr(status, flags);
+}
+
+__global__ void __launch_bounds__(256) quant_block_apply_kernel(
+    const __half *__restrict__ x, long long B, long long row_len, int blk, int batch_shared,
+    const unsigned int *__restrict__ ws, uint8_t *__restrict__ codes,
+    unsigned long long *__restrict__ ghist, int *__restrict__ status) {
+    __shared__ unsigned int shist[256];
+    const int tid = threadIdx.x;
+    const long long row = blockIdx.x, t = row / B, b = row % B;
+    const long long u = batch_shared ? t / blk : (t / blk) * B + b;
+    if (ghist) { for (int i = tid; i < 256; i += 256) shist[i] = 0; __syncthreads(); }
+    UnitParam p;
+    p.sf = __uint_as_float(ws[2 * u]); p.mi = __uint_as_float(ws[2 * u + 1]);
+    int flags = 0;
+    for (long long k = tid; k < row_len / 8; k += 256) {
+        uint4 v = *reinterpret_cast<const uint4 *>(x + row * row_len + k * 8);
+        uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist : nullptr);
+        *reinterpret_cast<uint2 *>(codes + row * row_len + k * 8) = o;
+    }
+    if (flags) atomicOr(status, flags);
+    if (ghist) hist_flush(shist, ghist, tid, 256);
+}
+
+// ---- dequantise: fp16((code + min_int) * scale), models/cache/kvcomp_encode.py:146 -------------
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict__ codes, kvc_qmeta_dev m,
+                                                      long long rows, long long B, long long H, int D,
+                                                      __half *__restrict__ out) {
+    // one thread = 8 consecutive channels of one (t, b, h) row
+    const long long per_row = D / 8;
+    long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= rows * per_row) return;
+    const long long row = i / per_row; const int c0 = (int)(i % per_row) * 8;
+    const long long h = row % H, b = (row / H) % B, t = row / (H * B);
+    const long long ub = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
+    uint2 cv = *reinterpret_cast<const uint2 *>(codes + row * D + c0);
+    const uint8_t *cb = reinterpret_cast<const uint8_t *>(&cv);
+    uint4 o; __half *oh = reinterpret_cast<__half *>(&o);
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        long long u = ub + (long long)(c0 + k) * m.sc;
+        float s = __half2float(__float2half_rn((float)((int)cb[k] + kvc_load_min(m, u))));
+        oh[k] = __float2half_rn(__fmul_rn(s, __half2float(m.scale[u])));
+    }
+    *reinterpret_cast<uint4 *>(out + row * D + c0) = o;
+}
+
+// ---- dense q.k over uncompressed K (kernels.cu:1192-1219), fp32 accumulation --------------------
+// One warp per (token, head) row of 128 fp16 values; lane = 4 channels.
+__global__ void __launch_bounds__(256) k_matvec_kernel(const __half *__restrict__ k, const __half *__restrict__ q,
+                                                       __half *__restrict__ out, long long rows, long long H) {
+    const int lane = threadIdx.x & 31;
+    long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    uint2 kv = *reinterpret_cast<const uint2 *>(k + row * 128 + lane * 4);
+    uint2 qv = *reinterpret_cast<const uint2 *>(q + (row % H) * 128 + lane * 4);
+    const __half2 *k2 = reinterpret_cast<const __half2 *>(&kv), *q2 = reinterpret_cast<const __half2 *>(&qv);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        float2 a = __half22float2(k2[i]), c = __half22float2(q2[i]);
+        acc = fmaf(a.x, c.x, acc); acc = fmaf(a.y, c.y, acc);
+    }
+    acc = kvc_warp_sum(acc);
+    if (lane == 0) out[row] = __float2half_rn(acc);
+}
+
+}  // namespace
+
+extern "C" int kvc_qmeta_make(int mode, int batch_shared, int64_t T, int64_t B, int64_t H, int64_t D,
+                              int64_t block, kvc_qmeta *q, int64_t *n_units) {
+    KVC_REQUIRE(q != nullptr, "kvc_qmeta_make: q is null");
+    KVC_REQUIRE(T >= 0 && B > 0 && H > 0 && D > 0, "kvc_qmeta_make: bad shape");
+    const int64_t nb = batch_shared ? 1 : B;
+    int64_t n = 0;
+    q->sj = q->sb = q->sh = q->sc = 0;
+    switch (mode) {
+    case KVC_MODE_BLOCK:
+        KVC_REQUIRE(block > 0 && T % block == 0, "kvc_qmeta_make: T=%lld is not a multiple of block=%lld", (long long)T, (long long)block);
+        q->tok_div = (int32_t)block; q->sj = nb; q->sb = batch_shared ? 0 : 1; n = (T / block) * nb; break;
+    case KVC_MODE_CHANNEL:
+        KVC_REQUIRE(block > 0 && T % block == 0, "kvc_qmeta_make: T=%lld is not a multiple of block=%lld", (long long)T, (long long)block);
+        q->tok_div = (int32_t)block; q->sj = B * H * D; q->sb = H * D; q->sh = D; q->sc = 1; n = (T / block) * B * H * D; break;
+    case KVC_MODE_TOKEN:
+        q->tok_div = 1; q->sj = nb; q->sb = batch_shared ? 0 : 1; n = T * nb; break;
+    case KVC_MODE_VECTOR:
+        q->tok_div = 1; q->sj = B * H; q->sb = H; q->sh = 1; n = T * B * H; break;
+    default:
+        KVC_REQUIRE(false, "kvc_qmeta_make: unknown mode %d", mode);
+    }
+    if (n_units) *n_units = n;
+    return KVC_OK;
+}
+
+extern "C" int64_t kvc_quantize_workspace(int mode, int batch_shared, int64_t T, int64_t B, int64_t block) {
+    if (mode != KVC_MODE_BLOCK || block <= 0) return 0;
+    return (T / block) * (batch_shared ? 1 : B) * 8;
+}
+
+extern "C" int kvc_quantize(const void *x, int64_t T, int64_t B, int64_t H, int64_t D,
+                            int mode, int batch_shared, int64_t block, float rel,
+                            uint8_t *codes, void *min_int, int min_bytes, void *scale,
+                            unsigned long long *hist, void *workspace, int64_t workspace_bytes,
+                            int32_t *status, kvc_stream_t stream) {
+    KVC_REQUIRE(x && codes && min_int && scale && status, "kvc_quantize: null pointer");
+    KVC_REQUIRE(T >= 0 && B > 0 && H > 0 && D > 0 && D % 8 == 0, "kvc_quantize: bad shape T=%lld B=%lld H=%lld D=%lld", (long long)T, (long long)B, (long long)H, (long long)D);
+    KVC_REQUIRE(min_bytes == 1 || min_bytes == 2, "kvc_quantize: min_bytes must be 1 or 2");
+    KVC_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(codes) & 7) == 0,
+                "kvc_quantize: x must be 16-byte and codes 8-byte aligned");
+    if (T == 0) return KVC_OK;
+    cudaStream_t s = kvc_cu(stream);
+    const __half *xh = reinterpret_cast<const __half *>(x);
+    __half *sc = reinterpret_cast<__half *>(scale);
+    switch (mode) {
+    case KVC_MODE_CHANNEL: {
+        KVC_REQUIRE(D == 128, "kvc_quantize: ChannelQuant needs head_dim 128");
+        KVC_REQUIRE(block > 0 && T % block == 0, "kvc_quantize: T=%lld is not a multiple of block=%lld", (long long)T, (long long)block);
+        long long tiles = (T / block) * B * H;
+        KVC_REQUIRE(tiles < (1ll << 31), "kvc_quantize: too many tiles");
+        quant_channel_kernel<<<(unsigned)tiles, 128, 0, s>>>(xh, B, H, (int)block, rel, codes, min_int, min_bytes, sc, hist, status);
+        break;
+    }
+    case KVC_MODE_TOKEN:
+    case KVC_MODE_VECTOR: {
+        long long ulen = mode == KVC_MODE_VECTOR ? D : (batch_shared ? B * H * D : H * D);
+        long long n_units = T * B * H * D / ulen;
+        if (ulen >= 2048) {
+            KVC_REQUIRE(n_units < (1ll << 31), "kvc_quantize: too many units");
+            quant_contig_kernel<256><<<(unsigned)n_units, 256, 0, s>>>(xh, n_units, ulen, rel, codes, min_int, min_bytes, sc, hist, status);
+        } else {
+            long long ctas = (n_units + 7) / 8;
+            KVC_REQUIRE(ctas < (1ll << 31), "kvc_quantize: too many units");
+            quant_contig_kernel<32><<<(unsigned)ctas, 256, 0, s>>>(xh, n_units, ulen, rel, codes, min_int, min_bytes, sc, hist, status);
+        }
+        break;
+    }
+    case KVC_MODE_BLOCK: {
+        KVC_REQUIRE(block > 0 && T % block == 0, "kvc_quantize: T=%lld is not a multiple of block=%lld", (long long)T, (long long)block);
+        long long n_units = (T / block) * (batch_shared ? 1 : B);
+        KVC_REQUIRE(workspace && workspace_bytes >= n_units * 8, "kvc_quantize: BlockQuant needs %lld bytes of workspace", n_units * 8);
+        KVC_REQUIRE(T * B < (1ll << 31), "kvc_quantize: too many rows");
+        unsigned int *ws = reinterpret_cast<unsigned int *>(workspace);
+        KVC_CUDA_OK(cudaMemsetAsync(ws, 0, n_units * 8, s));
+        quant_block_minmax_kernel<<<(unsigned)(T * B), 256, 0, s>>>(xh, B, H * D, (int)block, batch_shared, ws);
+        quant_block_finalize_kernel<<<(unsigned)((n_units + 127) / 128), 128, 0, s>>>(ws, n_units, rel, min_int, min_bytes, sc, status);
+        quant_block_apply_kernel<<<(unsigned)(T * B), 256, 0, s>>>(xh, B, H * D, (int)block, batch_shared, ws, codes, hist, status);
+        break;
+    }
+    default:
+        KVC_REQUIRE(false, "kvc_quantize: unknown mode %d", mode);
+    }
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}
+
+extern "C" int kvc_dequant(const uint8_t *codes, const kvc_qmeta *q, int64_t T, int64_t B, int64_t H, int64_t D,
+                           void *out, kvc_stream_t stream) {
+    KVC_REQUIRE(codes && q && q->min_int && q->scale && out, "kvc_dequant: null pointer");
+    KVC_REQUIRE(D > 0 && D % 8 == 0 && q->tok_div > 0, "kvc_dequant: bad shape");
+    KVC_REQUIRE(q->min_bytes == 1 || q->min_bytes == 2, "kvc_dequant: min_bytes must be 1 or 2");
+    long long rows = T * B * H, n = rows * (D / 8);
+    if (n == 0) return KVC_OK;
+    dequant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, kvc_cu(stream)>>>(codes, kvc_to_dev(*q), rows, B, H, (int)D,
+                                                                            reinterpret_cast<__half *>(out));
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}
+
+extern "C" int kvc_k_matvec(const void *k, const void *q, void *out, int64_t ctx, int64_t H, kvc_stream_t stream) {
+    KVC_REQUIRE(k && q && out, "kvc_k_matvec: null pointer");
+    KVC_REQUIRE(ctx >= 0 && H > 0, "kvc_k_matvec: bad shape");
+    long long rows = ctx * H;
+    if (rows == 0) return KVC_OK;
+    k_matvec_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, kvc_cu(stream)>>>(
+        reinterpret_cast<const __half *>(k), reinterpret_cast<const __half *>(q), reinterpret_cast<__half *>(out), rows, H);
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}

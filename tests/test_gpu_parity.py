@@ -1,0 +1,374 @@
+"""GPU parity: every kernel of libkvcomp_b200.so (called through the C ABI) against the CPU checker
+and the committed golden vectors.  Integer/byte results must be bit-exact; attention outputs must be
+within 1e-3 of the exact (double precision) value relative to the largest output magnitude."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kvc_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+ATTN_RTOL = 1e-3      # relative to max |out|; the tolerance BASELINE.json's north_star states
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from kvcomp_b200 import ops as _ops
+    return _ops
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def synth(T, B, H, seed=0, Hq=None):
+    from kvcomp_b200.synth import make_kv
+    k, v, q = make_kv(T, B, H, 128, seed=seed, device="cpu", Hq=Hq)
+    return k.numpy(), v.numpy(), q.numpy()
+
+
+MODE_CASES = [  # (tensor, mode, block, rel, batch_shared)
+    ("k", orc.MODE_BLOCK, 64, 0.05, True), ("k", orc.MODE_BLOCK, 64, 0.03, False),
+    ("k", orc.MODE_CHANNEL, 64, 0.05, False), ("k", orc.MODE_CHANNEL, 128, 0.02, False),
+    ("k", orc.MODE_CHANNEL, 64, 0.01, False),
+    ("v", orc.MODE_TOKEN, 128, 0.1, True), ("v", orc.MODE_TOKEN, 64, 0.05, False),
+    ("v", orc.MODE_TOKEN, 128, 0.15, False), ("v", orc.MODE_VECTOR, 64, 0.2, False),
+]
+
+
+@pytest.mark.parametrize("which,mode,block,rel,shared", MODE_CASES)
+def test_quantize_bit_exact(ops, which, mode, block, rel, shared):
+    k, v, _ = synth(256, 2, 4, seed=3)
+    x = k if which == "k" else v
+    codes, mi, sc, m, deg = orc.quant(x, mode, block, rel, shared)
+    hist = torch.zeros(256, dtype=torch.int64, device="cuda")
+    c2, mi2, sc2, spec, st = ops.quantize(dev(x), mode, block, rel, shared, min_dtype=torch.int16, hist=hist)
+    flags = ops.read_status(st)
+    assert np.array_equal(sc2.cpu().numpy().view(np.uint16), sc.view(np.uint16))
+    assert np.array_equal(mi2.cpu().numpy(), mi)
+    assert np.array_equal(c2.cpu().numpy(), codes)
+    assert np.array_equal(hist.cpu().numpy(), orc.histogram(codes))
+    assert (spec.tok_div, spec.sj, spec.sb, spec.sh, spec.sc) == (m.tok_div, m.sj, m.sb, m.sh, m.sc)
+    # int8 narrowing as the reference stores it
+    c3, mi8, _, _, st8 = ops.quantize(dev(x), mode, block, rel, shared, min_dtype=torch.int8)
+    assert np.array_equal(mi8.cpu().numpy(), orc.narrow_i8(mi))
+    assert bool(ops.read_status(st8) & 0x2) == bool(((mi < -128) | (mi > 127)).any())
+    assert flags & 0x4 == 0
+    # dequantised values
+    xh = ops.dequant(c2, mi2, sc2, spec).cpu().numpy()
+    assert np.array_equal(xh.view(np.uint16), orc.dequant(codes, mi, sc, m).view(np.uint16))
+
+
+def test_quantize_matches_reference_golden(ops, golden_dir):
+    z = np.load(os.path.join(golden_dir, "quant_golden.npz"))
+    meta = json.loads(bytes(z["cases_json"]).decode())
+    MODE = {"BlockQuant": 0, "ChannelQuant": 1, "TokenQuant": 2, "VectorQuant": 3}
+    for c in meta["cases"]:
+        if c["api"] == "quant":
+            mode, shared = (0 if c["dims"] == [1, 2, 3, 4] else 2), True
+        else:
+            mode, shared = MODE[c["mode"]], False
+        codes, mi, sc, _, st = ops.quantize(dev(z[c["src"]]), mode, c["block"], c["rel"], shared, min_dtype=torch.int16)
+        name = c["name"]
+        assert np.array_equal(codes.cpu().numpy(), z[name + "_codes"]), name
+        assert np.array_equal(sc.cpu().numpy().view(np.uint16), z[name + "_scale"].view(np.uint16)), name
+        assert np.array_equal(mi.cpu().numpy().astype(np.float32), z[name + "_min"].astype(np.float32)), name
+
+
+def test_quantize_matches_torch_ops_on_gpu(ops):
+    """The op sequence of utils/compute.py:93-106 evaluated by torch on CUDA fp16 tensors."""
+    k, v, _ = synth(128, 2, 4, seed=5)
+    for x, dims, blk, rel, mode in ((k, [1, 2, 3, 4], 64, 0.05, 0), (v, [2, 3, 4], 128, 0.1, 2)):
+        t = dev(x).view(-1, blk, 2, 4, 128)
+        mn, mx = t, t
+        for d in dims:
+            mn = mn.min(dim=d, keepdim=True).values
+            mx = mx.max(dim=d, keepdim=True).values
+        scale = (mx - mn) * rel
+        mi = (mn / scale).round_()
+        qi = (t / scale).round_() - mi
+        codes, mi2, sc2, _, _ = ops.quantize(dev(x), mode, blk, rel, True, min_dtype=torch.int16)
+        assert torch.equal(codes.view(-1), qi.to(torch.uint8).view(-1))
+        assert torch.equal(sc2.view(-1), scale.reshape(-1))
+        assert torch.equal(mi2.view(-1).float(), mi.reshape(-1).float())
+
+
+def test_zero_scale_unit_is_flagged(ops):
+    x = torch.ones(64, 1, 1, 128, dtype=torch.float16, device="cuda")
+    codes, mi, sc, _, st = ops.quantize(x, 0, 64, 0.05, True)
+    assert ops.read_status(st, raise_on_fatal=False) & 0x1
+    assert int(codes.max()) == 0
+
+
+def test_histogram(ops):
+    rng = np.random.default_rng(0)
+    for n in (1, 15, 16, 17, 4097, 1 << 20):
+        a = rng.integers(0, 40, n).astype(np.uint8)
+        h = ops.histogram(dev(a))
+        assert np.array_equal(h.cpu().numpy(), np.bincount(a, minlength=256))
+    # unaligned start, accumulation into an existing histogram
+    a = rng.integers(0, 256, 100003).astype(np.uint8)
+    t = dev(a)
+    h = ops.histogram(t[3:])
+    h = ops.histogram(t[:3], h)
+    assert np.array_equal(h.cpu().numpy(), np.bincount(a, minlength=256))
+
+
+def test_codebook_matches_reference_golden(ops, golden_dir):
+    with open(os.path.join(golden_dir, "huffman_golden.json")) as f:
+        cases = json.load(f)
+    for case in cases:
+        h = np.zeros(256, np.int64)
+        for s, c in case["counts"].items():
+            h[int(s)] = c
+        book = ops.build_codebook(dev(h))
+        hd = book.header()
+        enc = book.host()[64:64 + 2048].numpy().view(orc.ENC_DT)
+        assert orc.code_strings(enc) == {int(k): v for k, v in case["py_book"].items()}
+        assert hd["n_symbols"] == len(case["counts"]) and hd["flags"] == 0
+        oenc, _ = orc.gen_codes(h)
+        assert np.array_equal(book.ref_decode_tensor().numpy(), orc.ref_decode_tree(oenc))
+        if case["cpp_encode"] is not None:
+            shift, tab = book.ref_encode_tensor()
+            assert shift == case["cpp_shift"]
+            assert tab.numpy().tobytes().hex() == case["cpp_encode"]
+            assert book.ref_decode_tensor().numpy().tobytes().hex() == case["cpp_decode"]
+
+
+def _pipeline(ops, x, is_k, mode, block, rel, shared, min_dtype=torch.int16):
+    """quantise -> histogram -> book -> encode on the GPU; returns everything as device tensors."""
+    T, B, H, D = x.shape
+    hist = torch.zeros(256, dtype=torch.int64, device="cuda")
+    codes, mi, sc, spec, st = ops.quantize(dev(x), mode, block, rel, shared, min_dtype=min_dtype, hist=hist)
+    book = ops.build_codebook(hist)
+    bsz, tsz, _, cap = ops.buffer_sizes(T, B * H * D, is_k)
+    bi = torch.zeros(bsz, dtype=torch.uint8, device="cuda")
+    ti = torch.zeros(tsz // 2, dtype=torch.int16, device="cuda")
+    enc = torch.zeros(cap, dtype=torch.uint8, device="cuda")
+    total, st2 = ops.encode(codes, is_k, book.encode_table(), bi, ti, enc)
+    n = int(total.item())
+    assert ops.read_status(st2) & ~0x10 == 0
+    return dict(codes=codes, mi=mi, sc=sc, spec=spec, book=book, bi=bi, ti=ti, enc=enc, n=n, hist=hist)
+
+
+@pytest.mark.parametrize("is_k,mode,rel,T,B,H", [
+    (True, orc.MODE_BLOCK, 0.05, 256, 1, 4), (True, orc.MODE_CHANNEL, 0.05, 192, 2, 3),
+    (True, orc.MODE_CHANNEL, 0.01, 128, 1, 2), (False, orc.MODE_TOKEN, 0.1, 256, 1, 4),
+    (False, orc.MODE_TOKEN, 0.05, 384, 2, 3), (False, orc.MODE_TOKEN, 0.02, 128, 1, 2),
+])
+def test_encode_decode_bit_exact(ops, is_k, mode, rel, T, B, H):
+    k, v, _ = synth(T, B, H, seed=11)
+    x = k if is_k else v
+    shared = mode != orc.MODE_CHANNEL
+    r = _pipeline(ops, x, is_k, mode, 64 if is_k else 128, rel, shared)
+    codes = r["codes"].cpu().numpy()
+    oenc, _ = orc.gen_codes(orc.histogram(codes))
+    odata, obi, oti, ov = orc.encode(codes, is_k, oenc)
+    assert r["n"] == odata.size
+    assert np.array_equal(r["enc"][:r["n"]].cpu().numpy(), odata)
+    assert np.array_equal(r["bi"].cpu().numpy(), obi)
+    assert np.array_equal(r["ti"].cpu().numpy().view(np.uint16), oti)
+    out, st = ops.decode(r["enc"][:r["n"]], r["bi"], r["ti"], r["book"], T, B, H, is_k)
+    assert ops.read_status(st) == 0
+    assert np.array_equal(out.cpu().numpy(), codes)
+    # a stream written by the checker decodes on the GPU too
+    out2, st = ops.decode(dev(odata), dev(obi), dev(oti.view(np.int16)), r["book"], T, B, H, is_k)
+    assert ops.read_status(st) == 0 and np.array_equal(out2.cpu().numpy(), codes)
+
+
+def test_encode_base_offset_and_append(ops):
+    """Two store calls into one stream: the second call's block offsets carry the base offset
+    (kernels.cu:476) and the whole stream decodes as one cache."""
+    k, _, _ = synth(256, 1, 4, seed=2)
+    T, B, H = 256, 1, 4
+    codes, mi, sc, spec, _ = ops.quantize(dev(k), 0, 64, 0.05, True)
+    book = ops.build_codebook(ops.histogram(codes))
+    bi = torch.zeros(8 * (T // 64) * B * H, dtype=torch.uint8, device="cuda")
+    ti = torch.zeros(64 * (T // 64) * B * H, dtype=torch.int16, device="cuda")
+    enc = torch.zeros(T * B * H * 128, dtype=torch.uint8, device="cuda")
+    half = T // 2
+    nb = (half // 64) * B * H
+    t1, _ = ops.encode(codes[:half].contiguous(), True, book.encode_table(), bi[:8 * nb], ti[:64 * nb], enc)
+    n1 = int(t1.item())
+    t2, _ = ops.encode(codes[half:].contiguous(), True, book.encode_table(), bi[8 * nb:], ti[64 * nb:], enc[n1:], base_offset=n1)
+    n2 = int(t2.item())
+    out, st = ops.decode(enc[:n1 + n2], bi, ti, book, T, B, H, True)
+    assert ops.read_status(st) == 0 and torch.equal(out, codes)
+    off, _ = orc.block_infos(bi.cpu().numpy())
+    assert off[nb] == n1
+
+
+def test_book_from_reference_decode_tensor(ops):
+    k, _, _ = synth(128, 1, 2, seed=4)
+    r = _pipeline(ops, k, True, 0, 64, 0.05, True)
+    tree = r["book"].ref_decode_tensor().cuda()
+    book2 = ops.book_from_tree(tree)
+    assert torch.equal(book2.blob[64:], r["book"].blob[64:])
+    out, st = ops.decode(r["enc"][:r["n"]], r["bi"], r["ti"], book2, 128, 1, 2, True)
+    assert ops.read_status(st) == 0 and torch.equal(out, r["codes"])
+
+
+def test_frozen_book_flags_unseen_symbol(ops):
+    rng = np.random.default_rng(0)
+    codes = rng.integers(0, 4, (64, 1, 1, 128)).astype(np.uint8)
+    book = ops.build_codebook(ops.histogram(dev(codes)))
+    codes[3, 0, 0, 7] = 9
+    bi = torch.zeros(8, dtype=torch.uint8, device="cuda")
+    ti = torch.zeros(64, dtype=torch.int16, device="cuda")
+    enc = torch.zeros(8192, dtype=torch.uint8, device="cuda")
+    total, st = ops.encode(dev(codes), True, book.encode_table(), bi, ti, enc)
+    assert ops.read_status(st, raise_on_fatal=False) & 0x8
+    # bytes equal the checker's (which drops the symbol like the reference does)
+    enc_tab = book.host()[64:64 + 2048].numpy().view(orc.ENC_DT)
+    odata, _, oti, ov = orc.encode(codes, True, enc_tab)
+    assert ov[1] == 1
+    assert np.array_equal(enc[:int(total.item())].cpu().numpy(), odata)
+
+
+def test_long_codes_use_the_slow_path(ops):
+    """A very skewed alphabet has codes longer than the decode window; the stream still round-trips."""
+    rng = np.random.default_rng(1)
+    p = np.array([2.0 ** -(i + 1) for i in range(20)]); p[-1] = p[-2]; p /= p.sum()
+    codes = rng.choice(20, size=(128, 1, 2, 128), p=p).astype(np.uint8)
+    codes[5, 0, 1, :20] = np.arange(20)          # make sure every symbol occurs
+    for is_k in (True, False):
+        book = ops.build_codebook(ops.histogram(dev(codes)))
+        assert book.header()["max_len"] > 11
+        bi = torch.zeros(8 * 4, dtype=torch.uint8, device="cuda")
+        ti = torch.zeros(64 * 4, dtype=torch.int16, device="cuda")
+        enc = torch.zeros(codes.size, dtype=torch.uint8, device="cuda")
+        total, st = ops.encode(dev(codes), is_k, book.encode_table(), bi, ti, enc)
+        out, st2 = ops.decode(enc[:int(total.item())], bi, ti, book, 128, 1, 2, is_k)
+        assert ops.read_status(st) == 0 and ops.read_status(st2) == 0
+        assert np.array_equal(out.cpu().numpy(), codes)
+
+
+def _caches(ops, k, v, kmode, vmode, krel, vrel, kblock=64, shared=True, min_dtype=torch.int16):
+    T, B, H, _ = k.shape
+    rk = _pipeline(ops, k, True, kmode, kblock, krel, shared, min_dtype)
+    rv = _pipeline(ops, v, False, vmode, 128, vrel, shared, min_dtype)
+    kc = ops.make_cache(rk["enc"], rk["bi"], rk["ti"], rk["book"], rk["mi"], rk["sc"], rk["spec"], rk["n"])
+    vc = ops.make_cache(rv["enc"], rv["bi"], rv["ti"], rv["book"], rv["mi"], rv["sc"], rv["spec"], rv["n"])
+    return rk, rv, kc, vc
+
+
+def _oracle_q(r, T, B, H, mode, block, shared):
+    m, _ = orc.qmeta(mode, shared, T, B, H, 128, block)
+    return r["codes"].cpu().numpy(), r["mi"].cpu().numpy(), r["sc"].cpu().numpy(), m
+
+
+@pytest.mark.parametrize("kmode,shared,B,Hkv,Hq", [
+    (orc.MODE_BLOCK, True, 1, 4, 4), (orc.MODE_CHANNEL, False, 2, 2, 2), (orc.MODE_CHANNEL, False, 1, 2, 8),
+    (orc.MODE_BLOCK, False, 2, 2, 6), (orc.MODE_VECTOR, False, 1, 2, 2),
+])
+def test_fused_qk(ops, kmode, shared, B, Hkv, Hq):
+    T = 320
+    k, v, q = synth(T, B, Hkv, seed=7, Hq=Hq)
+    hist = torch.zeros(256, dtype=torch.int64, device="cuda")
+    r = _pipeline(ops, k, True, kmode, 64, 0.05, shared)
+    kc = ops.make_cache(r["enc"], r["bi"], r["ti"], r["book"], r["mi"], r["sc"], r["spec"], r["n"])
+    S, st = ops.fused_qk(kc, T, B, Hkv, dev(q), out_dtype=torch.float32)
+    assert ops.read_status(st) == 0
+    So = orc.qk(*_oracle_q(r, T, B, Hkv, kmode, 64, shared), q)
+    assert np.abs(S.cpu().numpy() - So).max() <= 1e-4 * np.abs(So).max()
+    # fp16 output, the reference's C tensor; its own tolerance is 1 % of max (test_py_ctx_k_2d_load.py:129-134)
+    S16, _ = ops.fused_qk(kc, T, B, Hkv, dev(q))
+    assert np.abs(S16.float().cpu().numpy() - So).max() <= 2e-3 * np.abs(So).max()
+
+
+@pytest.mark.parametrize("vmode,shared,B,Hkv,Hq", [
+    (orc.MODE_TOKEN, True, 1, 4, 4), (orc.MODE_TOKEN, False, 2, 2, 8), (orc.MODE_VECTOR, False, 1, 2, 4),
+])
+def test_fused_pv(ops, vmode, shared, B, Hkv, Hq):
+    T = 384
+    k, v, q = synth(T, B, Hkv, seed=8, Hq=Hq)
+    r = _pipeline(ops, v, False, vmode, 128, 0.1, shared)
+    vc = ops.make_cache(r["enc"], r["bi"], r["ti"], r["book"], r["mi"], r["sc"], r["spec"], r["n"])
+    rng = np.random.default_rng(3)
+    logits = rng.standard_normal((B, Hq, T)) * 2.5          # as test_py_ctx_v.py:62-67
+    P = np.exp(logits - logits.max(-1, keepdims=True)); P /= P.sum(-1, keepdims=True)
+    P16 = P.astype(np.float16)
+    part, st = ops.fused_pv(vc, T, B, Hkv, dev(P16))
+    assert ops.read_status(st) == 0 and part.shape == (T // 128, B, Hq, 128)
+    O = part.float().sum(0).cpu().numpy()
+    Oo = orc.pv(*_oracle_q(r, T, B, Hkv, vmode, 128, shared), P16.astype(np.float32))
+    assert np.abs(O - Oo).max() <= 2e-3 * np.abs(Oo).max()
+
+
+ATTN_CASES = [  # kmode, vmode, shared, T, B, Hkv, Hq, Tr, splits, min_dtype
+    (orc.MODE_CHANNEL, orc.MODE_TOKEN, False, 512, 1, 4, 4, 0, 0, torch.int16),
+    (orc.MODE_CHANNEL, orc.MODE_TOKEN, False, 640, 2, 2, 8, 0, 2, torch.int16),
+    (orc.MODE_BLOCK, orc.MODE_TOKEN, True, 1024, 1, 4, 4, 0, 3, torch.int8),
+    (orc.MODE_BLOCK, orc.MODE_TOKEN, True, 384, 2, 2, 2, 100, 1, torch.int8),
+    (orc.MODE_CHANNEL, orc.MODE_TOKEN, False, 896, 1, 2, 12, 300, 2, torch.int16),
+    (orc.MODE_CHANNEL, orc.MODE_VECTOR, False, 128, 3, 1, 1, 1, 0, torch.int16),
+]
+
+
+@pytest.mark.parametrize("kmode,vmode,shared,T,B,Hkv,Hq,Tr,splits,min_dtype", ATTN_CASES)
+def test_attn_decode(ops, kmode, vmode, shared, T, B, Hkv, Hq, Tr, splits, min_dtype):
+    k, v, q = synth(T + Tr, B, Hkv, seed=21, Hq=Hq)
+    rk, rv, kc, vc = _caches(ops, k[:T], v[:T], kmode, vmode, 0.05, 0.1, 64, shared, min_dtype)
+    scaling = 1.0 / math.sqrt(128)
+    kt = dev(k[T:]) if Tr else None
+    vt = dev(v[T:]) if Tr else None
+    out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits)
+    assert ops.read_status(st) == 0
+    ko = _oracle_q(rk, T, B, Hkv, kmode, 64, shared)
+    vo = _oracle_q(rv, T, B, Hkv, vmode, 128, shared)
+    O = orc.attention(*ko, *vo, q, scaling, k[T:] if Tr else None, v[T:] if Tr else None)
+    err = np.abs(out.float().cpu().numpy() - O).max() / np.abs(O).max()
+    assert err <= ATTN_RTOL, err
+    # a second call reuses a caller-held workspace and must give the same bits
+    ws = ops.attn_workspace(B, Hq, max(splits, ops.attn_splits(T, B, Hkv)), "cuda")
+    o1, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
+    o2, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
+    assert torch.equal(o1, o2) and torch.equal(o1, out)
+
+
+def test_attn_decode_config0(ops):
+    """Llama-2-7B single layer: 32 heads x 128, batch 1, 1024 tokens, K per channel / V per token in
+    64-token blocks at relative error bound 0.05, one decode step."""
+    T, B, H = 1024, 1, 32
+    k, v, q = synth(T, B, H, seed=0)
+    rk, rv, kc, vc = _caches(ops, k, v, orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.05, 0.05, 64, False)
+    scaling = 1.0 / math.sqrt(128)
+    out, st = ops.attn_decode(kc, vc, T, B, H, dev(q), scaling)
+    assert ops.read_status(st) == 0
+    O = orc.attention(*_oracle_q(rk, T, B, H, orc.MODE_CHANNEL, 64, False),
+                      *_oracle_q(rv, T, B, H, orc.MODE_TOKEN, 128, False), q, scaling)
+    assert np.abs(out.float().cpu().numpy() - O).max() <= ATTN_RTOL * np.abs(O).max()
+    # the two-call path (scores -> softmax -> partials) agrees as well
+    S, _ = ops.fused_qk(kc, T, B, H, dev(q), out_dtype=torch.float32)
+    P = torch.softmax(S * scaling, dim=-1).half()
+    part, _ = ops.fused_pv(vc, T, B, H, P)
+    O2 = part.float().sum(0).cpu().numpy()
+    assert np.abs(O2 - O).max() <= 2e-3 * np.abs(O).max()
+
+
+def test_k_matvec(ops):
+    rng = np.random.default_rng(0)
+    k = rng.standard_normal((192, 1, 8, 128)).astype(np.float16)
+    q = rng.standard_normal((1, 8, 128)).astype(np.float16)
+    out = torch.empty((192, 1, 8), dtype=torch.float16, device="cuda")
+    ops.k_matvec(dev(k), dev(q), out)
+    ref = orc.k_matvec(k, q)
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= 2e-3 * np.abs(ref).max()
+
+
+def test_errors_are_reported_not_fatal(ops):
+    from kvcomp_b200._lib import KvcError
+    x = torch.zeros(100, 1, 1, 128, dtype=torch.float16, device="cuda")
+    with pytest.raises(KvcError):
+        ops.quantize(x, 0, 64, 0.05)                      # T not a multiple of the block
+    with pytest.raises(KvcError):
+        ops.quantize(x.cpu(), 2, 64, 0.05)                # no CPU path
+    with pytest.raises(KvcError):
+        ops.buffer_sizes(100, 128, True)
