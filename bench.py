@@ -117,14 +117,14 @@ def build_layer(ops, torch, cfg, layer, seed, device):
         ti = torch.empty(tsz // 2, dtype=torch.int16, device=device)
         enc = torch.empty(cap, dtype=torch.uint8, device=device)
         total, st2 = ops.encode(codes, is_k, book.encode_table(), bi, ti, enc)
-        n = int(total.item())
+        n, maxb = (int(x) for x in total.tolist())
         ops.read_status(st, what="quantize"); ops.read_status(st2, what="encode")
         enc = enc[:n].clone()
         keep.append((enc, bi, ti, book, mi, sc))
-        caches.append(ops.make_cache(enc, bi, ti, book, mi, sc, spec, n))
+        caches.append(ops.make_cache(enc, bi, ti, book, mi, sc, spec, n, maxb))
         acct[name] = dict(encoded=n, block_info=bsz, thread_info=tsz,
                           quant_meta=mi.numel() * mi.element_size() + sc.numel() * 2,
-                          symbols=T * B * Hkv * 128, min_flag=ops.read_status(st, False))
+                          symbols=T * B * Hkv * 128, min_flag=ops.read_status(st, False), max_block=maxb)
         del codes, x
     del k, v
     return caches, keep, q, acct

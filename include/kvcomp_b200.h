@@ -85,6 +85,9 @@ typedef struct {
     const uint16_t *thread_info;  /* device */
     const void *book;             /* device, KVC_BOOK_BYTES, from kvc_build_codebook / kvc_book_from_tree */
     kvc_qmeta q;
+    int32_t max_block_bytes;      /* upper bound of any block's byte count (kvc_encode reports it); 0 = unknown
+                                     (8191 is assumed).  A tight bound lets more CTAs share an SM. */
+    int32_t reserved;
 } kvc_cache;
 
 /* ---- codebook object (device blob) ------------------------------------------------ */
@@ -92,8 +95,8 @@ typedef struct {
 #define KVC_BOOK_OFF_ENC    64                       /* 256 x {u32 code, u32 length}, symbol-indexed */
 #define KVC_BOOK_OFF_REFTREE (KVC_BOOK_OFF_ENC + 2048)   /* 512 x 3-byte nodes, reference format */
 #define KVC_BOOK_OFF_TREE   (KVC_BOOK_OFF_REFTREE + 1536) /* 512 x u32 wide nodes */
-#define KVC_BOOK_OFF_LUT    (KVC_BOOK_OFF_TREE + 2048)    /* (1<<KVC_LUT_BITS) x u32 */
-#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUT + 4 * (1 << KVC_LUT_BITS))
+#define KVC_BOOK_OFF_LUT    (KVC_BOOK_OFF_TREE + 2048)    /* (1<<KVC_LUT_BITS) x {u32 symbols, u32 advance} */
+#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUT + 8 * (1 << KVC_LUT_BITS))
 
 typedef struct {             /* first 32 bytes of the blob */
     int32_t n_symbols;       /* distinct symbols */
@@ -155,7 +158,8 @@ int kvc_book_from_tree(const uint8_t *ref_tree, int64_t tree_bytes, void *book, 
  * encode tensor, or book + KVC_BOOK_OFF_ENC with 256 entries).  block_info / thread_info:
  * this call's records (the caller offsets them for later store calls).  encoded: where
  * this call's bytes go; base_offset is added to the recorded block offsets
- * (kernels.cu:476).  total_bytes: device u64, receives the byte count of this call.
+ * (kernels.cu:476).  total_bytes: device u64[2]; [0] receives the byte count of this call,
+ * [1] is raised to the largest block byte count seen (zero it to start a new maximum).
  * workspace: kvc_encode_workspace() bytes. */
 int64_t kvc_encode_workspace(int64_t T, int64_t cols, int is_k);
 int kvc_encode(const uint8_t *codes, int64_t T, int64_t cols, int is_k,

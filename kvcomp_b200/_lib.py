@@ -27,7 +27,7 @@ BOOK_OFF_ENC = 64
 BOOK_OFF_REFTREE = BOOK_OFF_ENC + 2048
 BOOK_OFF_TREE = BOOK_OFF_REFTREE + 1536
 BOOK_OFF_LUT = BOOK_OFF_TREE + 2048
-BOOK_BYTES = BOOK_OFF_LUT + 4 * (1 << LUT_BITS)
+BOOK_BYTES = BOOK_OFF_LUT + 8 * (1 << LUT_BITS)
 
 
 class QMeta(C.Structure):
@@ -38,7 +38,8 @@ class QMeta(C.Structure):
 
 class Cache(C.Structure):
     _fields_ = [("encoded", C.c_void_p), ("encoded_bytes", C.c_int64), ("block_info", C.c_void_p),
-                ("thread_info", C.c_void_p), ("book", C.c_void_p), ("q", QMeta)]
+                ("thread_info", C.c_void_p), ("book", C.c_void_p), ("q", QMeta),
+                ("max_block_bytes", C.c_int32), ("reserved", C.c_int32)]
 
 
 class KvcError(RuntimeError):
@@ -85,9 +86,11 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB
-    if _build.is_stale():
-        path = _build.build()
+    path = os.environ.get("KVCOMP_B200_LIB")          # an alternative build of the same library
+    if not path:
+        path = _build.LIB
+        if _build.is_stale():
+            path = _build.build()
     if not os.path.exists(path):
         raise KvcError("libkvcomp_b200.so is missing and could not be built; there is no CPU fallback")
     lib = C.CDLL(path)

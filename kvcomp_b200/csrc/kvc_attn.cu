@@ -12,17 +12,26 @@
 //   V phase: thread = (128-token group, channel); its vector holds 128 tokens of that channel.
 //            out[ch] = sum_t code_t * ps[t] + zpv, with ps[t] = p[t]*scale[t] staged per group.
 // Both phases are "decode 128 symbols and dot them with a shared 128-vector", so they share one
-// decoder.  With grouped-query attention the G query heads of a KV head share every decode: the
-// weights are stored [position][G] and each symbol feeds G accumulators.
-// Accumulation is fp32 throughout (the reference accumulates in fp16).
+// decoder.  The shared vector is held in 16-bit block fixed point (one fp32 step per vector, value
+// = step * (256*hi + lo), hi signed and lo unsigned bytes): every table lookup yields up to four
+// symbols as four bytes, and two dp4a instructions multiply them with the four matching weight
+// bytes -- integer arithmetic, exact, accumulated in int32.  The only rounding is that of the
+// weights (2^-16 of the largest weight of the vector); the zero-point terms and everything after
+// the dot product are fp32.  With grouped-query attention the G query heads of a KV head share
+// every decode: weight records are stored [position][G].
 #include <math_constants.h>
 
 #include "kvc_decode.cuh"
 
+#ifndef KVC_DEBUG_SKIP
+#define KVC_DEBUG_SKIP 0
+#endif
+
 namespace {
 
-constexpr int SLOT_BYTES = 8192 + 32;
-constexpr int WROW = 132;                 // weight rows: 128 positions + zeroed overrun
+constexpr int SLOT_BYTES = 8192 + 32;     // a block is at most 8191 bytes (u16 fields) + alignment lead
+constexpr int SLOT_PAD = 1024;           // readable bytes behind the last staging slot
+constexpr int WROW = 132;                 // weight records per vector: 128 positions + zeroed overrun
 constexpr int NTHR = 256;
 
 struct CacheDev {
@@ -32,92 +41,161 @@ struct CacheDev {
     const uint16_t *thread_info;
     const void *book;
     kvc_qmeta_dev q;
+    uint32_t max_block;           // upper bound of a block's byte count
 };
 
 CacheDev to_dev(const kvc_cache &c) {
     CacheDev d;
+    d.max_block = (c.max_block_bytes > 0 && c.max_block_bytes < 8191) ? (uint32_t)c.max_block_bytes : 8191u;
     d.encoded = c.encoded; d.encoded_bytes = c.encoded_bytes;
     d.block_info = reinterpret_cast<const uint2 *>(c.block_info); d.thread_info = c.thread_info;
     d.book = c.book; d.q = kvc_to_dev(c.q);
     return d;
 }
 
-// acc[g] += f0*w[c][g] + f1*w[c+1][g] + f2*w[c+2][g]
-template <int G> __device__ __forceinline__ void fma3(float (&acc)[G], const float *wp, float f0, float f1, float f2);
-template <> __device__ __forceinline__ void fma3<1>(float (&acc)[1], const float *wp, float f0, float f1, float f2) {
-    acc[0] = fmaf(f0, wp[0], fmaf(f1, wp[1], fmaf(f2, wp[2], acc[0])));
+// ---- 16-bit fixed-point weight records -----------------------------------------------------------
+// record[c] = { hi bytes of w[c..c+3], lo bytes of w[c..c+3] }
+__device__ __forceinline__ uint2 pack4(int q0, int q1, int q2, int q3) {
+    uint2 r;
+    r.x = ((uint32_t)(q0 >> 8) & 0xffu) | (((uint32_t)(q1 >> 8) & 0xffu) << 8) |
+          (((uint32_t)(q2 >> 8) & 0xffu) << 16) | (((uint32_t)(q3 >> 8) & 0xffu) << 24);
+    r.y = ((uint32_t)q0 & 0xffu) | (((uint32_t)q1 & 0xffu) << 8) | (((uint32_t)q2 & 0xffu) << 16) | (((uint32_t)q3 & 0xffu) << 24);
+    return r;
 }
-template <> __device__ __forceinline__ void fma3<2>(float (&acc)[2], const float *wp, float f0, float f1, float f2) {
-    float2 a = *reinterpret_cast<const float2 *>(wp), b = *reinterpret_cast<const float2 *>(wp + 2),
-           c = *reinterpret_cast<const float2 *>(wp + 4);
-    acc[0] = fmaf(f0, a.x, fmaf(f1, b.x, fmaf(f2, c.x, acc[0])));
-    acc[1] = fmaf(f0, a.y, fmaf(f1, b.y, fmaf(f2, c.y, acc[1])));
-}
-template <> __device__ __forceinline__ void fma3<4>(float (&acc)[4], const float *wp, float f0, float f1, float f2) {
-    float4 a = *reinterpret_cast<const float4 *>(wp), b = *reinterpret_cast<const float4 *>(wp + 4),
-           c = *reinterpret_cast<const float4 *>(wp + 8);
-    acc[0] = fmaf(f0, a.x, fmaf(f1, b.x, fmaf(f2, c.x, acc[0])));
-    acc[1] = fmaf(f0, a.y, fmaf(f1, b.y, fmaf(f2, c.y, acc[1])));
-    acc[2] = fmaf(f0, a.z, fmaf(f1, b.z, fmaf(f2, c.z, acc[2])));
-    acc[3] = fmaf(f0, a.w, fmaf(f1, b.w, fmaf(f2, c.w, acc[3])));
+__device__ __forceinline__ float fix_step(float wmax) { return wmax > 0.f ? wmax * (1.0f / 32767.0f) : 0.f; }
+__device__ __forceinline__ int fix_quant(float w, float step) { return step > 0.f ? __float2int_rn(w / step) : 0; }
+__device__ __forceinline__ float fix_value(float step, int hi, int lo) { return step * fmaf((float)hi, 256.0f, (float)lo); }
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
-// decode the thread's vector and dot it with the weight rows at w ([WROW][G])
+// decode the thread's vector (staged at shared address slot_s) and dot it with the weight records at
+// shared address w_s ([WROW][G] records of 8 bytes)
+template <int G, bool ESC>
+__device__ __forceinline__ bool decode_dot_impl(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
+                                                uint32_t w_s, int (&hi)[G], int (&lo)[G]) {
+    return kvc_decode_vector<ESC>(slot_s, byte_pos, lut_s, tree_s, [&](uint32_t syms, uint32_t c8) {
+        if (G == 4) {
+            const uint4 a = lds128(w_s + c8 * 4), b = lds128(w_s + c8 * 4 + 16);
+            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, a.y, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(syms, a.z, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, a.w, lo[1 % G]);
+            hi[2 % G] = kvc_dp4a_us(syms, b.x, hi[2 % G]); lo[2 % G] = kvc_dp4a_uu(syms, b.y, lo[2 % G]);
+            hi[3 % G] = kvc_dp4a_us(syms, b.z, hi[3 % G]); lo[3 % G] = kvc_dp4a_uu(syms, b.w, lo[3 % G]);
+        } else if (G == 2) {
+            const uint4 a = lds128(w_s + c8 * 2);
+            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, a.y, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(syms, a.z, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, a.w, lo[1 % G]);
+        } else {
+            const uint2 a = kvc_lds64(w_s + c8);
+            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, a.y, lo[0]);
+        }
+    });
+}
+// esc: the book has codes longer than the table window (uniform over the CTA)
 template <int G>
-__device__ __forceinline__ bool decode_dot(const uint8_t *slot, uint32_t byte_pos, const KvcBookSmem &book,
-                                           const float *w, float (&acc)[G]) {
-    return kvc_decode_vector(reinterpret_cast<const uint32_t *>(slot), byte_pos, SLOT_BYTES / 4 - 1, book,
-                             [&](uint32_t s0, uint32_t s1, uint32_t s2, uint32_t, int c) {
-                                 fma3<G>(acc, w + c * G, (float)s0, (float)s1, (float)s2);
-                             });
+__device__ __forceinline__ bool decode_dot(const uint8_t *slot, uint32_t byte_pos, const KvcBookSmem &book, bool esc,
+                                           const uint2 *w, int (&hi)[G], int (&lo)[G]) {
+    const uint32_t slot_s = kvc_smem_addr(slot), lut_s = kvc_smem_addr(book.lut), tree_s = kvc_smem_addr(book.tree),
+                   w_s = kvc_smem_addr(w);
+    return esc ? decode_dot_impl<G, true>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo)
+               : decode_dot_impl<G, false>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo);
+}
+__device__ __forceinline__ bool book_has_long_codes(const void *book) {
+    return reinterpret_cast<const kvc_book_header *>(book)->max_len > KVC_LUT_BITS;
 }
 
-// stage the block `blk` of cache `kc` into `slot` with the 64 threads of a sub-group
+// ---- staging --------------------------------------------------------------------------------------
+// plain loads: the 64 threads of a sub-group copy block `blk` into `slot`
 __device__ __forceinline__ bool stage(const CacheDev &kc, long long blk, uint8_t *slot, uint32_t *lead, int v) {
     const uint2 bi = kc.block_info[blk];
     const uint32_t nbytes = bi.y & 0xffffu;
-    if (nbytes == 0 || nbytes > 8191u || (long long)bi.x + nbytes > kc.encoded_bytes) { *lead = 0; return false; }
+    if (nbytes == 0 || nbytes > kc.max_block || (long long)bi.x + nbytes > kc.encoded_bytes) { *lead = 0; return false; }
     *lead = kvc_stage_block(slot, kc.encoded, kc.encoded_bytes, bi.x, nbytes, v, 64);
     return true;
+}
+
+// bulk copies: lane `l` (< 4) of one warp issues the copy of its block; the whole warp must call.
+// The source range is widened to 16-byte boundaries; `encoded` is 16-byte aligned and readable to
+// the next boundary past its end (checked / required by the host code).
+__device__ __forceinline__ void stage_bulk(const CacheDev &kc, bool valid, long long blk, uint8_t *slot,
+                                           uint32_t *lead, int *ok, uint64_t *bar, int lane) {
+    uint32_t bytes = 0, ld = 0;
+    const uint8_t *a0 = nullptr;
+    bool good = false;
+    if (lane < 4 && valid) {
+        const uint2 bi = kc.block_info[blk];
+        const uint32_t nbytes = bi.y & 0xffffu;
+        good = nbytes != 0 && nbytes <= kc.max_block && (long long)bi.x + nbytes <= kc.encoded_bytes;
+        if (good) {
+            const uint8_t *src = kc.encoded + bi.x;
+            ld = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
+            a0 = src - ld;
+            bytes = (ld + nbytes + 15u) & ~15u;
+        }
+    }
+    uint32_t total = bytes;
+    total += __shfl_xor_sync(0xffffffffu, total, 1);
+    total += __shfl_xor_sync(0xffffffffu, total, 2);
+    if (lane == 0) kvc_mbar_expect_tx(bar, total);            // one arrival per phase, even for 0 bytes
+    __syncwarp();
+    if (lane < 4) {
+        lead[lane] = ld; ok[lane] = good;
+        if (bytes) kvc_bulk_g2s(slot, a0, bytes, bar);
+    }
 }
 
 __device__ __forceinline__ uint32_t vec_start(const uint16_t *thread_info, long long blk, int v) {
     return v ? (uint32_t)(thread_info[blk * 64 + v - 1] >> 3) : 0u;
 }
 
-// K weights of the 4 blocks of a 256-token tile: w[sub][c][g] and zp[sub][g].
+// ---- K weights --------------------------------------------------------------------------------------
+// Weight records of the 4 blocks of a 256-token tile: w[sub][c][g], step[sub][g], zp[sub][g].
+// One warp per (block, query head): lane = 4 consecutive channels.
 // Units that depend on the channel (sc != 0) need tok_div % 64 == 0 so that a block shares them;
-// otherwise scale and min_int are per-token scalars applied after the dot product.
+// otherwise scale and min_int are per-token scalars applied after the dot product (k_finish).
 template <int G>
-__device__ __forceinline__ void k_weights(float *w, float *zp, const float *qf, const kvc_qmeta_dev &m,
+__device__ __forceinline__ void k_weights(uint2 *w, float *step, float *zp, const float *qf, const kvc_qmeta_dev &m,
                                           long long tok0, long long T, long long b, long long h, int tid) {
-    for (int idx = tid; idx < 4 * WROW * G; idx += NTHR) {
-        const int sub = idx / (WROW * G), rem = idx - sub * (WROW * G), c = rem / G, g = rem - c * G;
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int pair = warp; pair < 4 * G; pair += NTHR / 32) {
+        const int sub = pair / G, g = pair - sub * G;
         const long long t = tok0 + sub * 64;
-        float val = 0.f;
-        if (c < 128 && t < T) {
-            val = qf[g * 128 + c];
-            if (m.sc != 0) {
-                const long long u = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh + (long long)c * m.sc;
-                val *= __half2float(m.scale[u]);
+        float wv[4] = {0.f, 0.f, 0.f, 0.f}, z = 0.f;
+        if (t < T) {
+            const long long ub = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int c = lane * 4 + i;
+                float q = qf[g * 128 + c];
+                if (m.sc != 0) {
+                    const long long u = ub + (long long)c * m.sc;
+                    const float sc = __half2float(m.scale[u]);
+                    z = fmaf((float)kvc_load_min(m, u) * sc, q, z);
+                    q *= sc;
+                }
+                wv[i] = q;
             }
         }
-        w[idx] = val;
-    }
-    if (m.sc != 0) {
-        const int lane = tid & 31, warp = tid >> 5;
-        for (int pair = warp; pair < 4 * G; pair += NTHR / 32) {
-            const int sub = pair / G, g = pair - sub * G;
-            const long long t = tok0 + sub * 64;
-            float s = 0.f;
-            if (t < T)
-                for (int c = lane; c < 128; c += 32) {
-                    const long long u = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh + (long long)c * m.sc;
-                    s = fmaf((float)kvc_load_min(m, u) * __half2float(m.scale[u]), qf[g * 128 + c], s);
-                }
-            s = kvc_warp_sum(s);
-            if (lane == 0) zp[pair] = s;
+        float mx = fmaxf(fmaxf(fabsf(wv[0]), fabsf(wv[1])), fmaxf(fabsf(wv[2]), fabsf(wv[3])));
+        mx = kvc_warp_max(mx);
+        z = kvc_warp_sum(z);
+        const float st = fix_step(mx);
+        int q4[7];
+#pragma unroll
+        for (int i = 0; i < 4; i++) q4[i] = fix_quant(wv[i], st);
+#pragma unroll
+        for (int i = 0; i < 3; i++) {                           // the next lane's first three values
+            int nv = __shfl_down_sync(0xffffffffu, q4[i], 1);
+            q4[4 + i] = lane == 31 ? 0 : nv;
         }
+        uint2 *row = w + (size_t)sub * WROW * G;
+#pragma unroll
+        for (int i = 0; i < 4; i++) row[(lane * 4 + i) * G + g] = pack4(q4[i], q4[i + 1], q4[i + 2], q4[i + 3]);
+        if (lane < WROW - 128) row[(128 + lane) * G + g] = make_uint2(0u, 0u);
+        if (lane == 0) { step[pair] = st; zp[pair] = z; }
     }
 }
 
@@ -137,19 +215,50 @@ __device__ __forceinline__ void load_q(float *qf, float *qsum, const __half *q, 
     }
 }
 
-// score of the thread's token from its decoded dot products
+// score of the thread's token from its integer dot products
 template <int G>
-__device__ __forceinline__ void k_finish(float (&acc)[G], const float *zp_sub, const float *qsum,
-                                         const kvc_qmeta_dev &m, long long t, long long b, long long h) {
+__device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], const int (&lo)[G], const float *step_sub,
+                                         const float *zp_sub, const float *qsum, const kvc_qmeta_dev &m,
+                                         long long t, long long b, long long h) {
     if (m.sc != 0) {
 #pragma unroll
-        for (int g = 0; g < G; g++) acc[g] += zp_sub[g];
+        for (int g = 0; g < G; g++) s[g] = fix_value(step_sub[g], hi[g], lo[g]) + zp_sub[g];
     } else {
         const long long u = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
         const float sc = __half2float(m.scale[u]), mi = (float)kvc_load_min(m, u);
 #pragma unroll
-        for (int g = 0; g < G; g++) acc[g] = sc * fmaf(mi, qsum[g], acc[g]);
+        for (int g = 0; g < G; g++) s[g] = sc * fmaf(mi, qsum[g], fix_value(step_sub[g], hi[g], lo[g]));
     }
+}
+
+// ---- V weights --------------------------------------------------------------------------------------
+// Called by all 256 threads (thread = token of the tile, grp = its 128-token group, tl = its index in
+// the group) with wv[g] = p[g] * scale of the token.  Builds records ps[grp][tl][g], step[grp][g].
+// `red` is scratch for 8*G floats, `q16` for 2*G*(128+4) int16.  Contains three block barriers.
+template <int G>
+__device__ __forceinline__ void v_weights(uint2 *ps, float *vstep, float *red, int16_t *q16, const float (&wv)[G],
+                                          int tid) {
+    const int lane = tid & 31, warp = tid >> 5, grp = tid >> 7, tl = tid & 127;
+#pragma unroll
+    for (int g = 0; g < G; g++) { float mx = kvc_warp_max(fabsf(wv[g])); if (lane == 0) red[warp * G + g] = mx; }
+    if (tl < 4) for (int g = 0; g < G; g++) q16[(grp * G + g) * 132 + 128 + tl] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const float mx = fmaxf(fmaxf(red[(grp * 4 + 0) * G + g], red[(grp * 4 + 1) * G + g]),
+                               fmaxf(red[(grp * 4 + 2) * G + g], red[(grp * 4 + 3) * G + g]));
+        const float st = fix_step(mx);
+        q16[(grp * G + g) * 132 + tl] = (int16_t)fix_quant(wv[g], st);
+        if (tl == 0) vstep[grp * G + g] = st;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const int16_t *qq = q16 + (grp * G + g) * 132 + tl;
+        ps[(grp * WROW + tl) * G + g] = pack4(qq[0], qq[1], qq[2], qq[3]);
+        if (tl < WROW - 128) ps[(grp * WROW + 128 + tl) * G + g] = make_uint2(0u, 0u);
+    }
+    __syncthreads();
 }
 
 // ---- fused K: raw scores ------------------------------------------------------------------------
@@ -157,7 +266,8 @@ template <int G>
 struct QkSmem {
     KvcBookSmem book;
     uint8_t slot[4][SLOT_BYTES];
-    float w[4 * WROW * G];
+    uint2 w[4 * WROW * G];
+    float step[4 * G];
     float zp[4 * G];
     float qf[G * 128];
     float qsum[G];
@@ -176,38 +286,41 @@ __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T
     const long long Gt = Hq / Hkv, hq0 = h * Gt + g0;
     const long long tok0 = (long long)blockIdx.x * 256, t = tok0 + tid;
     kvc_load_book(sm.book, kc.book, tid, NTHR);
+    const bool esc = book_has_long_codes(kc.book);
     load_q<G>(sm.qf, sm.qsum, q, b, Hq, hq0, 1.0f, tid);
     const long long blk = (tok0 / 64 + sub) * cols + col;
     const bool active = t < T;
     if (active) { uint32_t ld; bool ok = stage(kc, blk, sm.slot[sub], &ld, v); if (v == 0) { sm.lead[sub] = ld; sm.ok[sub] = ok; } }
     __syncthreads();
-    k_weights<G>(sm.w, sm.zp, sm.qf, kc.q, tok0, T, b, h, tid);
+    k_weights<G>(sm.w, sm.step, sm.zp, sm.qf, kc.q, tok0, T, b, h, tid);
     __syncthreads();
     if (!active) return;
-    float acc[G];
+    int hi[G], lo[G];
 #pragma unroll
-    for (int g = 0; g < G; g++) acc[g] = 0.f;
+    for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
     bool ok = sm.ok[sub];
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(kc.thread_info, blk, v), sm.book, sm.w + sub * WROW * G, acc);
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(kc.thread_info, blk, v), sm.book, esc, sm.w + sub * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
-    k_finish<G>(acc, sm.zp + sub * G, sm.qsum, kc.q, t, b, h);
+    float s[G];
+    k_finish<G>(s, hi, lo, sm.step + sub * G, sm.zp + sub * G, sm.qsum, kc.q, t, b, h);
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const long long o = (b * Hq + hq0 + g) * T + t;
-        if (out_f32) reinterpret_cast<float *>(out)[o] = acc[g];
-        else reinterpret_cast<__half *>(out)[o] = __float2half_rn(acc[g]);
+        if (out_f32) reinterpret_cast<float *>(out)[o] = s[g];
+        else reinterpret_cast<__half *>(out)[o] = __float2half_rn(s[g]);
     }
 }
 
 // ---- fused V: per-group partial outputs ----------------------------------------------------------
-// V weights of the 2 token groups of a tile: ps[grp][t][g] = P[t] * scale[t], zpv[grp][g].
 template <int G>
 struct PvSmem {
     KvcBookSmem book;
     uint8_t slot[4][SLOT_BYTES];
-    float ps[2 * WROW * G];
+    uint2 ps[2 * WROW * G];
+    float vstep[2 * G];
     float zpv[2 * G];
-    float red[8 * G];
+    float red[2][8 * G];
+    int16_t q16[2 * G * 132];
     uint32_t lead[4];
     int ok[4];
 };
@@ -225,12 +338,12 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
     const long long tok0 = (long long)blockIdx.x * 256, t = tok0 + tid;
     const kvc_qmeta_dev &m = vc.q;
     kvc_load_book(sm.book, vc.book, tid, NTHR);
+    const bool esc = book_has_long_codes(vc.book);
     const long long gI = tok0 / 128 + grp;
     const long long blk = gI * (cols * 2) + col * 2 + (ch >> 6);
     const bool active = gI * 128 < T;
     if (active) { uint32_t ld; bool ok = stage(vc, blk, sm.slot[sub], &ld, v); if (v == 0) { sm.lead[sub] = ld; sm.ok[sub] = ok; } }
-    // weights: thread = token
-    float zl[G];
+    float wv[G];
     {
         float sc = 0.f, mi = 0.f;
         if (t < T) {
@@ -239,46 +352,41 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
         }
 #pragma unroll
         for (int g = 0; g < G; g++) {
-            float p = t < T ? __half2float(P[(b * Hq + hq0 + g) * T + t]) : 0.f;
-            float w = p * sc;
-            sm.ps[(grp * WROW + ch) * G + g] = w;
-            zl[g] = kvc_warp_sum(w * mi);
+            const float p = t < T ? __half2float(P[(b * Hq + hq0 + g) * T + t]) : 0.f;
+            wv[g] = p * sc;
+            const float z = kvc_warp_sum(wv[g] * mi);
+            if (lane == 0) sm.red[1][warp * G + g] = z;
         }
-        if (ch < 4) for (int g = 0; g < G; g++) sm.ps[(grp * WROW + 128 + ch) * G + g] = 0.f;
-        if (lane == 0) for (int g = 0; g < G; g++) sm.red[warp * G + g] = zl[g];
     }
-    __syncthreads();
-    if (tid < 2 * G) {
-        const int gg = tid / G, g = tid - gg * G;
-        sm.zpv[tid] = sm.red[(gg * 4 + 0) * G + g] + sm.red[(gg * 4 + 1) * G + g] + sm.red[(gg * 4 + 2) * G + g] + sm.red[(gg * 4 + 3) * G + g];
-    }
-    __syncthreads();
+    v_weights<G>(sm.ps, sm.vstep, sm.red[0], sm.q16, wv, tid);
     if (!active) return;
-    float acc[G];
+    int hi[G], lo[G];
 #pragma unroll
-    for (int g = 0; g < G; g++) acc[g] = 0.f;
+    for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
     bool ok = sm.ok[sub];
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(vc.thread_info, blk, v), sm.book, sm.ps + grp * WROW * G, acc);
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(vc.thread_info, blk, v), sm.book, esc, sm.ps + grp * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
 #pragma unroll
-    for (int g = 0; g < G; g++)
-        out[((gI * B + b) * Hq + hq0 + g) * 128 + ch] = __float2half_rn(acc[g] + sm.zpv[grp * G + g]);
+    for (int g = 0; g < G; g++) {
+        const float z = sm.red[1][(grp * 4 + 0) * G + g] + sm.red[1][(grp * 4 + 1) * G + g] +
+                        sm.red[1][(grp * 4 + 2) * G + g] + sm.red[1][(grp * 4 + 3) * G + g];
+        out[((gI * B + b) * Hq + hq0 + g) * 128 + ch] = __float2half_rn(fix_value(sm.vstep[grp * G + g], hi[g], lo[g]) + z);
+    }
 }
 
 // ---- one-pass decode attention -------------------------------------------------------------------
 template <int G>
-struct AttnSmem {
-    KvcBookSmem bookK, bookV;
-    uint8_t slotK[4][SLOT_BYTES];
-    uint8_t slotV[4][SLOT_BYTES];
-    float w[4 * WROW * G];        // K weights; reused for the final cross-group sum
-    float ps[2 * WROW * G];
-    float zp[4 * G];
-    float zpv[2 * G];
+struct alignas(16) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch) and
+    KvcBookSmem bookK, bookV;         // SLOT_PAD bytes that a corrupt stream's decoder overrun may read
+    uint2 w[4 * WROW * G];            // K weight records; reused for the tail and the final cross-group sum
+    uint2 ps[2 * WROW * G];           // V weight records
+    float kstep[4 * G], zp[4 * G];
+    float vstep[2 * G];
     float qf[G * 128];
     float qsum[G];
-    float red[3][8 * G];          // per-warp max, sum, zpv partials
-    float alpha[G];
+    float red[4][8 * G];              // per-warp max, sum, zpv and weight-max partials
+    int16_t q16[2 * G * 132];
+    uint64_t bar[2];                  // K and V staging barriers
     uint32_t leadK[4], leadV[4];
     int okK[4], okV[4];
     int last;
@@ -291,15 +399,18 @@ struct AttnParams {
     __half *out;
     float scaling;
     int splits, tiles_per_split;
+    uint32_t slotK_bytes, slotV_bytes;   // capacity of one staging slot (multiple of 16)
     float *ws_part;               // [B*Hq][splits][130]: m, l, acc[128]
     int *ws_count;                // [B*Hq]
     int *status;
 };
 
-template <int G>
-__global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
+// BULK: stage with bulk asynchronous copies (one tile phase ahead) instead of plain loads.
+template <int G, bool BULK>
+__global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     AttnSmem<G> &sm = *reinterpret_cast<AttnSmem<G> *>(smem_raw);
+    uint8_t *const slotsK = smem_raw + sizeof(AttnSmem<G>), *const slotsV = slotsK + 4 * p.slotK_bytes;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
     const int grp = tid >> 7, ch = tid & 127;
     const long long T = p.T, B = p.B, Hkv = p.Hkv, Hq = p.Hq;
@@ -311,36 +422,66 @@ __global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
     long long tile_hi = tile_lo + p.tiles_per_split;
     if (tile_hi > n_tiles) tile_hi = n_tiles;
     const kvc_qmeta_dev &km = p.k.q, &vm = p.v.q;
+    int flags = 0;
 
+    // block ids of the tile's four K blocks / four V blocks for lane l < 4 of the issuing warp
+    auto blkK_of = [&](long long tile, int l) { return ((tile * 256) / 64 + l) * cols + col; };
+    auto blkV_of = [&](long long tile, int l) { return ((tile * 256) / 128 + (l >> 1)) * (cols * 2) + col * 2 + (l & 1); };
+    auto validK = [&](long long tile, int l) { return tile < tile_hi && tile * 256 + l * 64 < T; };
+    auto validV = [&](long long tile, int l) { return tile < tile_hi && tile * 256 + (l >> 1) * 128 < T; };
+
+    if (BULK) {
+        if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); }
+        __syncthreads();
+        if (warp == 0 && tile_lo < tile_hi) {
+            stage_bulk(p.k, validK(tile_lo, lane & 3), blkK_of(tile_lo, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
+            stage_bulk(p.v, validV(tile_lo, lane & 3), blkV_of(tile_lo, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
+        }
+    }
     kvc_load_book(sm.bookK, p.k.book, tid, NTHR);
     kvc_load_book(sm.bookV, p.v.book, tid, NTHR);
+    const bool escK = book_has_long_codes(p.k.book), escV = book_has_long_codes(p.v.book);
     load_q<G>(sm.qf, sm.qsum, p.q, b, Hq, hq0, p.scaling, tid);
 
     float m_run[G], l_run[G], acc[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
-    int flags = 0;
 
-    for (long long tile = tile_lo; tile < tile_hi; tile++) {
+    uint32_t phase = 0;
+    for (long long tile = tile_lo; tile < tile_hi; tile++, phase ^= 1u) {
         const long long tok0 = tile * 256, t = tok0 + tid;
         const long long blkK = (tok0 / 64 + sub) * cols + col;
         const long long gI = tok0 / 128 + grp;
         const long long blkV = gI * (cols * 2) + col * 2 + (ch >> 6);
         const bool actK = t < T, actV = gI * 128 < T;
-        __syncthreads();                                   // slots, weights and reductions are free
-        if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, sm.slotK[sub], &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
-        if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, sm.slotV[sub], &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
-        k_weights<G>(sm.w, sm.zp, sm.qf, km, tok0, T, b, h, tid);
+        __syncthreads();                                   // weights, reductions (and unbuffered slots) are free
+        // per-thread metadata of this tile, requested early so that the loads overlap the weight build
+        const uint32_t startK = actK ? vec_start(p.k.thread_info, blkK, v) : 0u;
+        const uint32_t startV = actV ? vec_start(p.v.thread_info, blkV, v) : 0u;
+        float vsc = 0.f, vmi = 0.f;
+        if (actK) {
+            const long long u = (t / vm.tok_div) * vm.sj + b * vm.sb + h * vm.sh;
+            vsc = __half2float(vm.scale[u]); vmi = (float)kvc_load_min(vm, u);
+        }
+        if (!BULK) {
+            if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
+            if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
+        }
+        k_weights<G>(sm.w, sm.kstep, sm.zp, sm.qf, km, tok0, T, b, h, tid);
+        if (BULK && !kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
         __syncthreads();
         // ---- K: scores of this tile's tokens
         float s[G];
-#pragma unroll
-        for (int g = 0; g < G; g++) s[g] = 0.f;
         if (actK) {
+            int hi[G], lo[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okK[sub];
-            if (ok) ok = decode_dot<G>(sm.slotK[sub], sm.leadK[sub] + vec_start(p.k.thread_info, blkK, v), sm.bookK, sm.w + sub * WROW * G, s);
+#if !(KVC_DEBUG_SKIP & 1)
+            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + startK, sm.bookK, escK, sm.w + sub * WROW * G, hi, lo);
+#endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
-            k_finish<G>(s, sm.zp + sub * G, sm.qsum, km, t, b, h);
+            k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km, t, b, h);
         } else {
 #pragma unroll
             for (int g = 0; g < G; g++) s[g] = -CUDART_INF_F;
@@ -348,13 +489,10 @@ __global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
         // ---- online softmax over the tile
 #pragma unroll
         for (int g = 0; g < G; g++) { float mx = kvc_warp_max(s[g]); if (lane == 0) sm.red[0][warp * G + g] = mx; }
-        __syncthreads();
-        float vsc = 0.f, vmi = 0.f;
-        if (actK) {
-            const long long u = (t / vm.tok_div) * vm.sj + b * vm.sb + h * vm.sh;
-            vsc = __half2float(vm.scale[u]); vmi = (float)kvc_load_min(vm, u);
-        }
-        float alpha[G];
+        __syncthreads();                                   // also: every thread is done with the K slots
+        if (BULK && warp == 0)                             // next tile's K blocks land during the V phase
+            stage_bulk(p.k, validK(tile + 1, lane & 3), blkK_of(tile + 1, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
+        float alpha[G], wv[G];
 #pragma unroll
         for (int g = 0; g < G; g++) {
             float mt = sm.red[0][g];
@@ -364,13 +502,11 @@ __global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
             alpha[g] = __expf(m_run[g] - m_new);           // exp(-inf) = 0 on the first tile
             const float pr = actK ? __expf(s[g] - m_new) : 0.f;
             m_run[g] = m_new;
-            const float wv = pr * vsc;
-            sm.ps[(grp * WROW + ch) * G + g] = wv;
-            const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv * vmi);
+            wv[g] = pr * vsc;
+            const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * vmi);
             if (lane == 0) { sm.red[1][warp * G + g] = ssum; sm.red[2][warp * G + g] = zsum; }
         }
-        if (ch < 4) for (int g = 0; g < G; g++) sm.ps[(grp * WROW + 128 + ch) * G + g] = 0.f;
-        __syncthreads();
+        v_weights<G>(sm.ps, sm.vstep, sm.red[3], sm.q16, wv, tid);      // three barriers inside
 #pragma unroll
         for (int g = 0; g < G; g++) {
             float lt = 0.f;
@@ -378,25 +514,42 @@ __global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
             for (int w8 = 0; w8 < 8; w8++) lt += sm.red[1][w8 * G + g];
             l_run[g] = l_run[g] * alpha[g] + lt;
         }
+        if (BULK && !kvc_mbar_wait(&sm.bar[1], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
         // ---- V: accumulate this tile's contribution for the thread's (group, channel)
         float dv[G];
 #pragma unroll
         for (int g = 0; g < G; g++) dv[g] = 0.f;
         if (actV) {
+            int hi[G], lo[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okV[sub];
-            if (ok) ok = decode_dot<G>(sm.slotV[sub], sm.leadV[sub] + vec_start(p.v.thread_info, blkV, v), sm.bookV, sm.ps + grp * WROW * G, dv);
+#if !(KVC_DEBUG_SKIP & 2)
+            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + startV, sm.bookV, escV, sm.ps + grp * WROW * G, hi, lo);
+#endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
 #pragma unroll
             for (int g = 0; g < G; g++)
-                dv[g] += sm.red[2][(grp * 4 + 0) * G + g] + sm.red[2][(grp * 4 + 1) * G + g] +
-                         sm.red[2][(grp * 4 + 2) * G + g] + sm.red[2][(grp * 4 + 3) * G + g];
+                dv[g] = fix_value(sm.vstep[grp * G + g], hi[g], lo[g]) +
+                        sm.red[2][(grp * 4 + 0) * G + g] + sm.red[2][(grp * 4 + 1) * G + g] +
+                        sm.red[2][(grp * 4 + 2) * G + g] + sm.red[2][(grp * 4 + 3) * G + g];
         }
 #pragma unroll
         for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
+        if (BULK) {
+            __syncthreads();                               // every thread is done with the V slots
+            if (warp == 0)                                 // next tile's V blocks land during its K phase
+                stage_bulk(p.v, validV(tile + 1, lane & 3), blkV_of(tile + 1, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
+        }
+    }
+    if (BULK && tile_lo < tile_hi) {      // the copies issued for the tile after the last one are empty, but their phase must end
+        if (!kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
+        if (!kvc_mbar_wait(&sm.bar[1], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
     }
 
     // ---- uncompressed tail (the recent window), handled by the last split: dense fp16 rows
     if (p.Tr > 0 && split == p.splits - 1) {
+        float *pt = reinterpret_cast<float *>(sm.w);           // p[row][g] for 256 rows
         for (long long r0 = 0; r0 < p.Tr; r0 += 256) {
             const long long r = r0 + tid;
             const bool act = r < p.Tr;
@@ -421,7 +574,6 @@ __global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
             for (int g = 0; g < G; g++) { float mx = kvc_warp_max(s[g]); if (lane == 0) sm.red[0][warp * G + g] = mx; }
             __syncthreads();
             float alpha[G];
-            float *pt = sm.w;                                  // p[t][g] for the 256 rows
 #pragma unroll
             for (int g = 0; g < G; g++) {
                 float mt = sm.red[0][g];
@@ -461,7 +613,7 @@ __global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
 
     // ---- combine the two token groups of the CTA, then the splits
     __syncthreads();
-    float *sumbuf = sm.w;                                      // [2][128][G]
+    float *sumbuf = reinterpret_cast<float *>(sm.w);           // [2][128][G]
 #pragma unroll
     for (int g = 0; g < G; g++) sumbuf[(grp * 128 + ch) * G + g] = acc[g];
     __syncthreads();
@@ -515,6 +667,7 @@ __global__ void __launch_bounds__(NTHR, 2) attn_decode_kernel(AttnParams p) {
 template <class K>
 int set_smem(K kernel, size_t bytes) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) { kvc_set_error("cudaFuncSetAttribute(%zu bytes) failed: %s", bytes, cudaGetErrorString(e)); return KVC_ERR_CUDA; }
     return KVC_OK;
 }
@@ -640,17 +793,25 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     p.ws_count = reinterpret_cast<int *>(workspace);
     p.ws_part = workspace ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) + ((B * Hq * 4 + 255) / 256) * 256) : nullptr;
     p.status = status;
+    // a slot holds the largest block plus its alignment lead, widened to 16-byte chunks, plus the
+    // decoder's two words of read-ahead
+    p.slotK_bytes = ((p.k.max_block + 15u + 15u) & ~15u) + 16u;
+    p.slotV_bytes = ((p.v.max_block + 15u + 15u) & ~15u) + 16u;
+    const size_t slot_total = 4 * (size_t)(p.slotK_bytes + p.slotV_bytes) + SLOT_PAD;
+    // bulk copies widen every block to 16-byte boundaries: both streams must start on one
+    const bool bulk = (reinterpret_cast<uintptr_t>(k->encoded) & 15) == 0 && (reinterpret_cast<uintptr_t>(v->encoded) & 15) == 0;
     const dim3 grid((unsigned)splits, (unsigned)(B * Hkv));
     const long long Gt = Hq / Hkv;
     for (long long g0 = 0; g0 < Gt;) {
         const int G = next_chunk(Gt - g0);
         p.g0 = g0;
-#define KVC_AT(GG)                                                                                              \
+#define KVC_AT(GG, BB)                                                                                          \
     {                                                                                                           \
-        if (int rc = set_smem(attn_decode_kernel<GG>, sizeof(AttnSmem<GG>))) return rc;                         \
-        attn_decode_kernel<GG><<<grid, NTHR, sizeof(AttnSmem<GG>), kvc_cu(stream)>>>(p);                        \
+        if (int rc = set_smem(attn_decode_kernel<GG, BB>, slot_total + sizeof(AttnSmem<GG>))) return rc;        \
+        attn_decode_kernel<GG, BB><<<grid, NTHR, slot_total + sizeof(AttnSmem<GG>), kvc_cu(stream)>>>(p);       \
     }
-        if (G == 4) KVC_AT(4) else if (G == 2) KVC_AT(2) else KVC_AT(1)
+        if (bulk) { if (G == 4) KVC_AT(4, true) else if (G == 2) KVC_AT(2, true) else KVC_AT(1, true) }
+        else { if (G == 4) KVC_AT(4, false) else if (G == 2) KVC_AT(2, false) else KVC_AT(1, false) }
 #undef KVC_AT
         g0 += G;
     }

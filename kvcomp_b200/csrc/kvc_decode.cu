@@ -13,7 +13,7 @@ constexpr int TILE_STRIDE = 132;
 struct DecodeSmem {
     KvcBookSmem book;
     uint8_t slot[4][SLOT_BYTES];
-    uint8_t tile[4][64 * TILE_STRIDE];
+    uint8_t tile[4][64 * TILE_STRIDE];      // also the padding a corrupt stream's overrun reads land in
 };
 
 __global__ void __launch_bounds__(256) decode_kernel(
@@ -43,12 +43,15 @@ __global__ void __launch_bounds__(256) decode_kernel(
             uint8_t *trow = sm.tile[sub] + v * TILE_STRIDE;
             bool ok = start < nbytes;
             if (ok)
-                ok = kvc_decode_vector(reinterpret_cast<const uint32_t *>(sm.slot[sub]), lead + start, SLOT_BYTES / 4 - 1, sm.book,
-                                       [&](uint32_t s0, uint32_t s1, uint32_t s2, uint32_t ns, int c) {
-                                           if (c < 128) trow[c] = (uint8_t)s0;
-                                           if (ns > 1 && c + 1 < 128) trow[c + 1] = (uint8_t)s1;
-                                           if (ns > 2 && c + 2 < 128) trow[c + 2] = (uint8_t)s2;
-                                       });
+                ok = kvc_decode_vector<true>(kvc_smem_addr(sm.slot[sub]), lead + start, kvc_smem_addr(sm.book.lut),
+                                             kvc_smem_addr(sm.book.tree),
+                                             [&](uint32_t syms, uint32_t c8) {
+                                                 // four byte stores; bytes past the lookup's symbols are rewritten by
+                                                 // the next lookup, bytes past position 127 land in the row padding
+                                                 uint8_t *d = trow + (c8 >> 3);
+                                                 d[0] = (uint8_t)syms; d[1] = (uint8_t)(syms >> 8);
+                                                 d[2] = (uint8_t)(syms >> 16); d[3] = (uint8_t)(syms >> 24);
+                                             });
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
         }
         __syncthreads();

@@ -1,9 +1,10 @@
-// Per-thread Huffman vector decoder shared by the plain decoder and the fused attention kernels.
+// Per-thread Huffman vector decoder shared by the plain decoder and the fused attention kernels,
+// and the helpers that stage compressed blocks in shared memory.
 //
 // A vector is 128 symbols, MSB-first, starting on a byte boundary (kernels.cu:237-291 walks it
 // one bit at a time through a tree in global memory).  Here the block's bytes sit in shared
 // memory, the thread keeps 64 bits of the stream in two registers and looks up KVC_LUT_BITS
-// bits at a time in a shared-memory table that returns up to three symbols per lookup; codes
+// bits at a time in a shared-memory table that returns up to four symbols per lookup; codes
 // longer than the window continue bit by bit from the tree node the window leads to.
 #pragma once
 
@@ -11,7 +12,7 @@
 
 struct KvcBookSmem {                      // per-CTA copy of the decode structures of one book
     uint32_t tree[512];
-    uint32_t lut[KVC_LUT_SIZE];
+    uint2 lut[KVC_LUT_SIZE];
 };
 
 __device__ __forceinline__ void kvc_load_book(KvcBookSmem &b, const void *book, int tid, int nthr) {
@@ -44,46 +45,102 @@ __device__ __forceinline__ uint32_t kvc_stage_block(uint8_t *slot, const uint8_t
     return lead;
 }
 
-// Decode one vector.  sw: the slot as 32-bit words; byte_pos: where the vector starts in the slot.
-// emit(s0, s1, s2, ns, c) receives up to three symbols (unused ones are 0) for positions c..c+ns-1;
-// it may be handed symbols beyond position 127 at the very end of the vector and must ignore them.
-// Every iteration advances by at least one symbol, so the loop ends after at most 128 rounds.
-// Word reads are clamped to max_word (the last word of the slot), so a corrupt stream can make the
-// result wrong but never the access.  Returns false when the bits do not form valid codes.
-template <class Emit>
-__device__ __forceinline__ bool kvc_decode_vector(const uint32_t *__restrict__ sw, uint32_t byte_pos,
-                                                  uint32_t max_word, const KvcBookSmem &book, Emit emit) {
-    uint32_t wi = min(byte_pos >> 2, max_word - 1), p = (byte_pos & 3u) << 3;
-    uint32_t hi = kvc_bswap(sw[wi]), lo = kvc_bswap(sw[wi + 1]);
-    wi += 2;
-    int c = 0;
+// ---- bulk asynchronous copies (TMA, untiled) completing on a shared-memory mbarrier -------------
+__device__ __forceinline__ uint32_t kvc_smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void kvc_mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(kvc_smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void kvc_mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void kvc_mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(kvc_smem_addr(bar)), "r"(bytes) : "memory");
+}
+// src and dst 16-byte aligned, bytes a multiple of 16 and > 0
+__device__ __forceinline__ void kvc_bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(kvc_smem_addr(dst)), "l"(src), "r"(bytes), "r"(kvc_smem_addr(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity.  Returns false if it never completed.
+__device__ __forceinline__ bool kvc_mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t a = kvc_smem_addr(bar);
+    for (int it = 0; it < (1 << 22); it++) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(a), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ int kvc_dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int kvc_dp4a_uu(uint32_t a_u8x4, uint32_t b_u8x4, int c) {
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_u8x4), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t kvc_lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// Decode one vector.  slot_s: shared-space address of the staged block (16-byte aligned); byte_pos:
+// where the vector starts in it; lut_s / tree_s: shared-space addresses of the book's tables.
+// The decoder state is (position << 16) | bit offset into the (hi, lo) register pair, so applying a
+// table entry is one add and (state >> 13) is position * 8 whatever the bit offset is.
+// emit(syms, c8): `syms` holds up to four symbols, one per byte, for positions c..c+3 of the vector
+// (unused bytes are 0), c8 = c * 8 (the byte offset of an 8-byte weight record).  At the very end of
+// a vector it may be handed symbols for positions beyond 127; the consumer keeps room for them.
+// ESC = false is for books whose longest code fits the table window: no escape test in the loop.
+// Every round advances by at least one symbol, so the loop ends after at most 128 rounds; a corrupt
+// stream can read at most a few hundred bytes past its vector, for which the kernels keep padding
+// behind the last slot.  Returns false when the bits do not form valid codes.
+template <bool ESC, class Emit>
+__device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
+                                                  Emit emit) {
+    uint32_t ptr = slot_s + (byte_pos & ~3u);
+    uint32_t state = (byte_pos & 3u) << 3;
+    uint32_t hi = kvc_bswap(kvc_lds32(ptr)), lo = kvc_bswap(kvc_lds32(ptr + 4));
+    uint32_t nxt = kvc_lds32(ptr + 8);     // one word of read-ahead keeps the refill off the critical path
+    ptr += 12;
     bool ok = true;
-    while (c < KVC_VEC_LEN) {
-        const uint32_t win = __funnelshift_l(lo, hi, p);
-        const uint32_t e = book.lut[win >> (32 - KVC_LUT_BITS)];
-        const uint32_t ns = (e >> 4) & 3u;
-        if (ns != 0) {
-            emit((e >> 8) & 0xffu, (e >> 16) & 0xffu, e >> 24, ns, c);
-            c += ns;
-            p += e & 15u;
-        } else {                                       // code longer than the window
-            uint32_t node = e >> 8, sym = 0;
+    do {
+        const uint32_t win = __funnelshift_l(lo, hi, state);          // the shift uses the low 5 bits
+        const uint2 e = kvc_lds64(lut_s + ((win >> (32 - KVC_LUT_BITS - 3)) & ((KVC_LUT_SIZE - 1) << 3)));
+        if (!ESC || e.y != 0) {
+            emit(e.x, state >> 13);
+            state += e.y;
+        } else {                                                      // code longer than the window
+            uint32_t node = e.x, sym = 0;
             bool found = false;
-            p += KVC_LUT_BITS;
+            const uint32_t c8 = state >> 13;
+            state += KVC_LUT_BITS;
             for (int guard = 0; guard < 40; guard++) {
-                if (p >= 32) { hi = lo; lo = kvc_bswap(sw[min(wi, max_word)]); wi++; p -= 32; }
+                if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
                 if (node >= 512u) break;
-                const uint32_t nd = book.tree[node];
+                const uint32_t nd = kvc_lds32(tree_s + node * 4);
                 if ((nd & 0xffffu) == KVC_TREE_LEAF) { sym = nd >> 16; found = true; break; }
-                const uint32_t bit = __funnelshift_l(lo, hi, p) >> 31;
-                p++;
+                const uint32_t bit = __funnelshift_l(lo, hi, state) >> 31;
+                state += 1u;
                 node = (nd >> (16 * bit)) & 0xffffu;
             }
             ok = ok && found;
-            emit(sym, 0u, 0u, 1u, c);
-            c += 1;
+            emit(sym, c8);
+            state += 1u << 16;
         }
-        if (p >= 32) { hi = lo; lo = kvc_bswap(sw[min(wi, max_word)]); wi++; p -= 32; }
-    }
+        if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
+    } while (state < (KVC_VEC_LEN << 16));
     return ok;
 }

@@ -62,7 +62,7 @@ __device__ __forceinline__ uint32_t warp_excl_scan(uint32_t v, int lane, uint32_
 __global__ void __launch_bounds__(256) encode_sizes_kernel(
     const uint8_t *__restrict__ codes, long long cols, int is_k, const uint32_t *__restrict__ enc, int n_entries,
     uint16_t *__restrict__ thread_info, uint32_t *__restrict__ sizes, unsigned long long *__restrict__ partial,
-    int *__restrict__ status) {
+    unsigned long long *__restrict__ max_block, int *__restrict__ status) {
     __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE];
     __shared__ EncTable tab;
     __shared__ uint32_t vbits[64];
@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(256) encode_sizes_kernel(
         if (lane == 0) {
             sizes[blk] = total;
             atomicAdd(&partial[blk >> 10], (unsigned long long)total);
+            if (max_block) atomicMax(max_block, (unsigned long long)total);
             if (total > 8191u) flags |= KVC_FLAG_BLOCK_LONG;
         }
     }
@@ -257,7 +258,8 @@ extern "C" int kvc_encode(const uint8_t *codes, int64_t T, int64_t cols, int is_
         reinterpret_cast<uint8_t *>(workspace) + ((nblk * 4 + 15) / 16) * 16);
     const uint32_t *enc = reinterpret_cast<const uint32_t *>(enc_table);
     KVC_CUDA_OK(cudaMemsetAsync(partial, 0, (n_part + 1) * 8, s));
-    encode_sizes_kernel<<<(unsigned)nblk, 256, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info, sizes, partial, status);
+    encode_sizes_kernel<<<(unsigned)nblk, 256, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info, sizes, partial,
+                                                      total_bytes ? total_bytes + 1 : nullptr, status);
     scan_partials_kernel<<<1, 1024, 0, s>>>(partial, n_part, total_bytes);
     scan_blocks_kernel<<<(unsigned)n_part, 1024, 0, s>>>(sizes, nblk, partial, base_offset, encoded_capacity,
                                                         reinterpret_cast<uint2 *>(block_info), status);

@@ -191,8 +191,9 @@ def book_from_tree(ref_tree):
 
 def encode(codes, is_k, enc_table, block_info, thread_info, encoded, base_offset=0, status=None, total=None):
     """codes u8 [T,B,H,128] -> writes block_info (u8, 8 B per block), thread_info (2 B per vector) and
-    encoded (u8) in place; returns (total device int64[1], status).  enc_table: device uint8 tensor
-    of {u32 code, u32 length} entries indexed by symbol."""
+    encoded (u8) in place; returns (total, status) where total is a device int64[2]: [0] the byte count
+    of this call, [1] the largest block byte count (a running maximum when `total` is passed in again).
+    enc_table: device uint8 tensor of {u32 code, u32 length} entries indexed by symbol."""
     lib = _lib.load()
     _cuda(codes, torch.uint8, "codes")
     T, B, H, D = codes.shape
@@ -201,7 +202,7 @@ def encode(codes, is_k, enc_table, block_info, thread_info, encoded, base_offset
     cols = B * H
     dev = codes.device
     status = new_status(dev) if status is None else status
-    total = torch.zeros(1, dtype=torch.int64, device=dev) if total is None else total
+    total = torch.zeros(2, dtype=torch.int64, device=dev) if total is None else total
     ws = torch.empty(max(lib.kvc_encode_workspace(T, cols, int(is_k)), 16), dtype=torch.uint8, device=dev)
     _cuda(enc_table, torch.uint8, "encode_code_book")
     for t, n in ((block_info, "block_infos"), (thread_info, "thread_infos"), (encoded, "encoded_data")):
@@ -229,11 +230,11 @@ def decode(encoded, block_info, thread_info, book, T, B, H, is_k, out=None, stat
     return out, status
 
 
-def make_cache(encoded, block_info, thread_info, book, min_int, scale, spec, encoded_bytes=None):
+def make_cache(encoded, block_info, thread_info, book, min_int, scale, spec, encoded_bytes=None, max_block_bytes=0):
     """The kvc_cache argument of the fused kernels.  The tensors must stay alive during the call."""
     n = encoded.numel() if encoded_bytes is None else int(encoded_bytes)
     return Cache(encoded.data_ptr(), n, block_info.data_ptr(), thread_info.data_ptr(), book.blob.data_ptr(),
-                 spec.qmeta(min_int, scale))
+                 spec.qmeta(min_int, scale), int(max_block_bytes), 0)
 
 
 def fused_qk(cache, T, B, Hkv, q, out=None, out_dtype=torch.float16, status=None):

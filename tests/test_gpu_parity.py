@@ -153,9 +153,11 @@ def _pipeline(ops, x, is_k, mode, block, rel, shared, min_dtype=torch.int16):
     ti = torch.zeros(tsz // 2, dtype=torch.int16, device="cuda")
     enc = torch.zeros(cap, dtype=torch.uint8, device="cuda")
     total, st2 = ops.encode(codes, is_k, book.encode_table(), bi, ti, enc)
-    n = int(total.item())
+    n, maxb = (int(x) for x in total.tolist())
     assert ops.read_status(st2) & ~0x10 == 0
-    return dict(codes=codes, mi=mi, sc=sc, spec=spec, book=book, bi=bi, ti=ti, enc=enc, n=n, hist=hist)
+    _, nb = orc.block_infos(bi.cpu().numpy())
+    assert maxb == int(nb.max())
+    return dict(codes=codes, mi=mi, sc=sc, spec=spec, book=book, bi=bi, ti=ti, enc=enc, n=n, hist=hist, maxb=maxb)
 
 
 @pytest.mark.parametrize("is_k,mode,rel,T,B,H", [
@@ -196,9 +198,9 @@ def test_encode_base_offset_and_append(ops):
     half = T // 2
     nb = (half // 64) * B * H
     t1, _ = ops.encode(codes[:half].contiguous(), True, book.encode_table(), bi[:8 * nb], ti[:64 * nb], enc)
-    n1 = int(t1.item())
+    n1 = int(t1[0].item())
     t2, _ = ops.encode(codes[half:].contiguous(), True, book.encode_table(), bi[8 * nb:], ti[64 * nb:], enc[n1:], base_offset=n1)
-    n2 = int(t2.item())
+    n2 = int(t2[0].item())
     out, st = ops.decode(enc[:n1 + n2], bi, ti, book, T, B, H, True)
     assert ops.read_status(st) == 0 and torch.equal(out, codes)
     off, _ = orc.block_infos(bi.cpu().numpy())
@@ -229,7 +231,7 @@ def test_frozen_book_flags_unseen_symbol(ops):
     enc_tab = book.host()[64:64 + 2048].numpy().view(orc.ENC_DT)
     odata, _, oti, ov = orc.encode(codes, True, enc_tab)
     assert ov[1] == 1
-    assert np.array_equal(enc[:int(total.item())].cpu().numpy(), odata)
+    assert np.array_equal(enc[:int(total[0].item())].cpu().numpy(), odata)
 
 
 def test_long_codes_use_the_slow_path(ops):
@@ -245,17 +247,17 @@ def test_long_codes_use_the_slow_path(ops):
         ti = torch.zeros(64 * 4, dtype=torch.int16, device="cuda")
         enc = torch.zeros(codes.size, dtype=torch.uint8, device="cuda")
         total, st = ops.encode(dev(codes), is_k, book.encode_table(), bi, ti, enc)
-        out, st2 = ops.decode(enc[:int(total.item())], bi, ti, book, 128, 1, 2, is_k)
+        out, st2 = ops.decode(enc[:int(total[0].item())], bi, ti, book, 128, 1, 2, is_k)
         assert ops.read_status(st) == 0 and ops.read_status(st2) == 0
         assert np.array_equal(out.cpu().numpy(), codes)
 
 
-def _caches(ops, k, v, kmode, vmode, krel, vrel, kblock=64, shared=True, min_dtype=torch.int16):
+def _caches(ops, k, v, kmode, vmode, krel, vrel, kblock=64, shared=True, min_dtype=torch.int16, tight=True):
     T, B, H, _ = k.shape
     rk = _pipeline(ops, k, True, kmode, kblock, krel, shared, min_dtype)
     rv = _pipeline(ops, v, False, vmode, 128, vrel, shared, min_dtype)
-    kc = ops.make_cache(rk["enc"], rk["bi"], rk["ti"], rk["book"], rk["mi"], rk["sc"], rk["spec"], rk["n"])
-    vc = ops.make_cache(rv["enc"], rv["bi"], rv["ti"], rv["book"], rv["mi"], rv["sc"], rv["spec"], rv["n"])
+    kc = ops.make_cache(rk["enc"], rk["bi"], rk["ti"], rk["book"], rk["mi"], rk["sc"], rk["spec"], rk["n"], rk["maxb"] if tight else 0)
+    vc = ops.make_cache(rv["enc"], rv["bi"], rv["ti"], rv["book"], rv["mi"], rv["sc"], rv["spec"], rv["n"], rv["maxb"] if tight else 0)
     return rk, rv, kc, vc
 
 
@@ -277,7 +279,8 @@ def test_fused_qk(ops, kmode, shared, B, Hkv, Hq):
     S, st = ops.fused_qk(kc, T, B, Hkv, dev(q), out_dtype=torch.float32)
     assert ops.read_status(st) == 0
     So = orc.qk(*_oracle_q(r, T, B, Hkv, kmode, 64, shared), q)
-    assert np.abs(S.cpu().numpy() - So).max() <= 1e-4 * np.abs(So).max()
+    # the shared weight vector is held in 16-bit block fixed point: errors of a few 1e-4 of max
+    assert np.abs(S.cpu().numpy() - So).max() <= 5e-4 * np.abs(So).max()
     # fp16 output, the reference's C tensor; its own tolerance is 1 % of max (test_py_ctx_k_2d_load.py:129-134)
     S16, _ = ops.fused_qk(kc, T, B, Hkv, dev(q))
     assert np.abs(S16.float().cpu().numpy() - So).max() <= 2e-3 * np.abs(So).max()
@@ -331,6 +334,27 @@ def test_attn_decode(ops, kmode, vmode, shared, T, B, Hkv, Hq, Tr, splits, min_d
     o1, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
     o2, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
     assert torch.equal(o1, o2) and torch.equal(o1, out)
+
+
+def test_attn_decode_unaligned_stream_and_unknown_bound(ops):
+    """Streams that do not start on a 16-byte boundary take the plain-load staging path; an unknown
+    block bound falls back to the format's maximum.  Same bits either way."""
+    T, B, Hkv, Hq = 512, 2, 2, 4
+    k, v, q = synth(T, B, Hkv, seed=31, Hq=Hq)
+    rk, rv, kc, vc = _caches(ops, k, v, orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.05, 0.1, 64, False)
+    scaling = 1.0 / math.sqrt(128)
+    out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=2)
+    assert ops.read_status(st) == 0
+    rk0, rv0, kc0, vc0 = _caches(ops, k, v, orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.05, 0.1, 64, False, tight=False)
+    out0, st = ops.attn_decode(kc0, vc0, T, B, Hkv, dev(q), scaling, splits=2)
+    assert ops.read_status(st) == 0 and torch.equal(out, out0)
+    # shift both streams by 3 bytes
+    ek = torch.zeros(rk["n"] + 64, dtype=torch.uint8, device="cuda"); ek[3:3 + rk["n"]] = rk["enc"][:rk["n"]]
+    ev = torch.zeros(rv["n"] + 64, dtype=torch.uint8, device="cuda"); ev[3:3 + rv["n"]] = rv["enc"][:rv["n"]]
+    kc1 = ops.make_cache(ek[3:], rk["bi"], rk["ti"], rk["book"], rk["mi"], rk["sc"], rk["spec"], rk["n"], rk["maxb"])
+    vc1 = ops.make_cache(ev[3:], rv["bi"], rv["ti"], rv["book"], rv["mi"], rv["sc"], rv["spec"], rv["n"], rv["maxb"])
+    out1, st = ops.attn_decode(kc1, vc1, T, B, Hkv, dev(q), scaling, splits=2)
+    assert ops.read_status(st) == 0 and torch.equal(out, out1)
 
 
 def test_attn_decode_config0(ops):
