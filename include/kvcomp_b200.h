@@ -91,12 +91,12 @@ typedef struct {
 } kvc_cache;
 
 /* ---- codebook object (device blob) ------------------------------------------------ */
-#define KVC_LUT_BITS        11
+#define KVC_LUT_BITS        12
 #define KVC_BOOK_OFF_ENC    64                       /* 256 x {u32 code, u32 length}, symbol-indexed */
 #define KVC_BOOK_OFF_REFTREE (KVC_BOOK_OFF_ENC + 2048)   /* 512 x 3-byte nodes, reference format */
 #define KVC_BOOK_OFF_TREE   (KVC_BOOK_OFF_REFTREE + 1536) /* 512 x u32 wide nodes */
-#define KVC_BOOK_OFF_LUT    (KVC_BOOK_OFF_TREE + 2048)    /* (1<<KVC_LUT_BITS) x {u32 symbols, u32 advance} */
-#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUT + 8 * (1 << KVC_LUT_BITS))
+#define KVC_BOOK_OFF_LUT    (KVC_BOOK_OFF_TREE + 2048)    /* (1<<KVC_LUT_BITS) x u32 decode-table entries */
+#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUT + 4 * (1 << KVC_LUT_BITS))
 
 typedef struct {             /* first 32 bytes of the blob */
     int32_t n_symbols;       /* distinct symbols */

@@ -22,12 +22,12 @@ FATAL_FLAGS = FLAG_CODE_OVERFLOW | FLAG_SYMBOL_MISSING | FLAG_BLOCK_LONG | FLAG_
 
 MODE_BLOCK, MODE_CHANNEL, MODE_TOKEN, MODE_VECTOR = 0, 1, 2, 3
 
-LUT_BITS = 11
+LUT_BITS = 12
 BOOK_OFF_ENC = 64
 BOOK_OFF_REFTREE = BOOK_OFF_ENC + 2048
 BOOK_OFF_TREE = BOOK_OFF_REFTREE + 1536
 BOOK_OFF_LUT = BOOK_OFF_TREE + 2048
-BOOK_BYTES = BOOK_OFF_LUT + 8 * (1 << LUT_BITS)
+BOOK_BYTES = BOOK_OFF_LUT + 4 * (1 << LUT_BITS)
 
 
 class QMeta(C.Structure):

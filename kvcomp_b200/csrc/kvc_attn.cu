@@ -54,7 +54,7 @@ CacheDev to_dev(const kvc_cache &c) {
 }
 
 // ---- 16-bit fixed-point weight records -----------------------------------------------------------
-// record[c] = { hi bytes of w[c..c+3], lo bytes of w[c..c+3] }
+// per position c: a word of the hi bytes of w[c..c+3] and a word of their lo bytes (pack4 gives {hi, lo})
 __device__ __forceinline__ uint2 pack4(int q0, int q1, int q2, int q3) {
     uint2 r;
     r.x = ((uint32_t)(q0 >> 8) & 0xffu) | (((uint32_t)(q1 >> 8) & 0xffu) << 8) |
@@ -72,32 +72,33 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
-// decode the thread's vector (staged at shared address slot_s) and dot it with the weight records at
-// shared address w_s ([WROW][G] records of 8 bytes)
+// decode the thread's vector (staged at shared address slot_s) and dot it with the weight words at
+// shared address w_s: WROW x G words of hi bytes followed by WROW x G words of lo bytes
 template <int G, bool ESC>
 __device__ __forceinline__ bool decode_dot_impl(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
                                                 uint32_t w_s, int (&hi)[G], int (&lo)[G]) {
-    return kvc_decode_vector<ESC>(slot_s, byte_pos, lut_s, tree_s, [&](uint32_t syms, uint32_t c8) {
+    constexpr uint32_t LO = WROW * G * 4;
+    return kvc_decode_vector<ESC>(slot_s, byte_pos, lut_s, tree_s, [&](uint32_t syms, uint32_t c4) {
         if (G == 4) {
-            const uint4 a = lds128(w_s + c8 * 4), b = lds128(w_s + c8 * 4 + 16);
-            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, a.y, lo[0]);
-            hi[1 % G] = kvc_dp4a_us(syms, a.z, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, a.w, lo[1 % G]);
-            hi[2 % G] = kvc_dp4a_us(syms, b.x, hi[2 % G]); lo[2 % G] = kvc_dp4a_uu(syms, b.y, lo[2 % G]);
-            hi[3 % G] = kvc_dp4a_us(syms, b.z, hi[3 % G]); lo[3 % G] = kvc_dp4a_uu(syms, b.w, lo[3 % G]);
+            const uint4 a = lds128(w_s + c4 * 4), b = lds128(w_s + c4 * 4 + LO);
+            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, b.x, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(syms, a.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, b.y, lo[1 % G]);
+            hi[2 % G] = kvc_dp4a_us(syms, a.z, hi[2 % G]); lo[2 % G] = kvc_dp4a_uu(syms, b.z, lo[2 % G]);
+            hi[3 % G] = kvc_dp4a_us(syms, a.w, hi[3 % G]); lo[3 % G] = kvc_dp4a_uu(syms, b.w, lo[3 % G]);
         } else if (G == 2) {
-            const uint4 a = lds128(w_s + c8 * 2);
-            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, a.y, lo[0]);
-            hi[1 % G] = kvc_dp4a_us(syms, a.z, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, a.w, lo[1 % G]);
+            const uint2 a = kvc_lds64(w_s + c4 * 2), b = kvc_lds64(w_s + c4 * 2 + LO);
+            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, b.x, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(syms, a.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, b.y, lo[1 % G]);
         } else {
-            const uint2 a = kvc_lds64(w_s + c8);
-            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, a.y, lo[0]);
+            hi[0] = kvc_dp4a_us(syms, kvc_lds32(w_s + c4), hi[0]);
+            lo[0] = kvc_dp4a_uu(syms, kvc_lds32(w_s + c4 + LO), lo[0]);
         }
     });
 }
 // esc: the book has codes longer than the table window (uniform over the CTA)
 template <int G>
 __device__ __forceinline__ bool decode_dot(const uint8_t *slot, uint32_t byte_pos, const KvcBookSmem &book, bool esc,
-                                           const uint2 *w, int (&hi)[G], int (&lo)[G]) {
+                                           const uint32_t *w, int (&hi)[G], int (&lo)[G]) {
     const uint32_t slot_s = kvc_smem_addr(slot), lut_s = kvc_smem_addr(book.lut), tree_s = kvc_smem_addr(book.tree),
                    w_s = kvc_smem_addr(w);
     return esc ? decode_dot_impl<G, true>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo)
@@ -157,7 +158,7 @@ __device__ __forceinline__ uint32_t vec_start(const uint16_t *thread_info, long 
 // Units that depend on the channel (sc != 0) need tok_div % 64 == 0 so that a block shares them;
 // otherwise scale and min_int are per-token scalars applied after the dot product (k_finish).
 template <int G>
-__device__ __forceinline__ void k_weights(uint2 *w, float *step, float *zp, const float *qf, const kvc_qmeta_dev &m,
+__device__ __forceinline__ void k_weights(uint32_t *w, float *step, float *zp, const float *qf, const kvc_qmeta_dev &m,
                                           long long tok0, long long T, long long b, long long h, int tid) {
     const int lane = tid & 31, warp = tid >> 5;
     for (int pair = warp; pair < 4 * G; pair += NTHR / 32) {
@@ -191,10 +192,13 @@ __device__ __forceinline__ void k_weights(uint2 *w, float *step, float *zp, cons
             int nv = __shfl_down_sync(0xffffffffu, q4[i], 1);
             q4[4 + i] = lane == 31 ? 0 : nv;
         }
-        uint2 *row = w + (size_t)sub * WROW * G;
+        uint32_t *row = w + (size_t)sub * 2 * WROW * G;           // hi words, then lo words
 #pragma unroll
-        for (int i = 0; i < 4; i++) row[(lane * 4 + i) * G + g] = pack4(q4[i], q4[i + 1], q4[i + 2], q4[i + 3]);
-        if (lane < WROW - 128) row[(128 + lane) * G + g] = make_uint2(0u, 0u);
+        for (int i = 0; i < 4; i++) {
+            const uint2 r = pack4(q4[i], q4[i + 1], q4[i + 2], q4[i + 3]);
+            row[(lane * 4 + i) * G + g] = r.x; row[WROW * G + (lane * 4 + i) * G + g] = r.y;
+        }
+        if (lane < WROW - 128) { row[(128 + lane) * G + g] = 0u; row[WROW * G + (128 + lane) * G + g] = 0u; }
         if (lane == 0) { step[pair] = st; zp[pair] = z; }
     }
 }
@@ -236,7 +240,7 @@ __device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], cons
 // the group) with wv[g] = p[g] * scale of the token.  Builds records ps[grp][tl][g], step[grp][g].
 // `red` is scratch for 8*G floats, `q16` for 2*G*(128+4) int16.  Contains three block barriers.
 template <int G>
-__device__ __forceinline__ void v_weights(uint2 *ps, float *vstep, float *red, int16_t *q16, const float (&wv)[G],
+__device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red, int16_t *q16, const float (&wv)[G],
                                           int tid) {
     const int lane = tid & 31, warp = tid >> 5, grp = tid >> 7, tl = tid & 127;
 #pragma unroll
@@ -255,8 +259,10 @@ __device__ __forceinline__ void v_weights(uint2 *ps, float *vstep, float *red, i
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const int16_t *qq = q16 + (grp * G + g) * 132 + tl;
-        ps[(grp * WROW + tl) * G + g] = pack4(qq[0], qq[1], qq[2], qq[3]);
-        if (tl < WROW - 128) ps[(grp * WROW + 128 + tl) * G + g] = make_uint2(0u, 0u);
+        uint32_t *row = ps + (size_t)grp * 2 * WROW * G;          // hi words, then lo words
+        const uint2 r = pack4(qq[0], qq[1], qq[2], qq[3]);
+        row[tl * G + g] = r.x; row[WROW * G + tl * G + g] = r.y;
+        if (tl < WROW - 128) { row[(128 + tl) * G + g] = 0u; row[WROW * G + (128 + tl) * G + g] = 0u; }
     }
     __syncthreads();
 }
@@ -266,7 +272,7 @@ template <int G>
 struct QkSmem {
     KvcBookSmem book;
     uint8_t slot[4][SLOT_BYTES];
-    uint2 w[4 * WROW * G];
+    uint32_t w[4 * 2 * WROW * G];
     float step[4 * G];
     float zp[4 * G];
     float qf[G * 128];
@@ -299,7 +305,7 @@ __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T
 #pragma unroll
     for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
     bool ok = sm.ok[sub];
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(kc.thread_info, blk, v), sm.book, esc, sm.w + sub * WROW * G, hi, lo);
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(kc.thread_info, blk, v), sm.book, esc, sm.w + sub * 2 * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
     float s[G];
     k_finish<G>(s, hi, lo, sm.step + sub * G, sm.zp + sub * G, sm.qsum, kc.q, t, b, h);
@@ -316,7 +322,7 @@ template <int G>
 struct PvSmem {
     KvcBookSmem book;
     uint8_t slot[4][SLOT_BYTES];
-    uint2 ps[2 * WROW * G];
+    uint32_t ps[2 * 2 * WROW * G];
     float vstep[2 * G];
     float zpv[2 * G];
     float red[2][8 * G];
@@ -364,7 +370,7 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
 #pragma unroll
     for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
     bool ok = sm.ok[sub];
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(vc.thread_info, blk, v), sm.book, esc, sm.ps + grp * WROW * G, hi, lo);
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(vc.thread_info, blk, v), sm.book, esc, sm.ps + grp * 2 * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
 #pragma unroll
     for (int g = 0; g < G; g++) {
@@ -378,8 +384,8 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
 template <int G>
 struct alignas(16) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch) and
     KvcBookSmem bookK, bookV;         // SLOT_PAD bytes that a corrupt stream's decoder overrun may read
-    uint2 w[4 * WROW * G];            // K weight records; reused for the tail and the final cross-group sum
-    uint2 ps[2 * WROW * G];           // V weight records
+    uint32_t w[4 * 2 * WROW * G];     // K weight words; reused for the tail and the final cross-group sum
+    uint32_t ps[2 * 2 * WROW * G];    // V weight words
     float kstep[4 * G], zp[4 * G];
     float vstep[2 * G];
     float qf[G * 128];
@@ -446,6 +452,13 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
     float m_run[G], l_run[G], acc[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
+#ifdef KVC_DEBUG_DELAY
+    {
+        const unsigned lin = blockIdx.y * gridDim.x + blockIdx.x;
+        const unsigned slot = (lin / 148u) % 3u;
+        for (unsigned i = 0; i < slot * KVC_DEBUG_DELAY; i++) __nanosleep(1000);
+    }
+#endif
 
     uint32_t phase = 0;
     for (long long tile = tile_lo; tile < tile_hi; tile++, phase ^= 1u) {
@@ -478,7 +491,7 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okK[sub];
 #if !(KVC_DEBUG_SKIP & 1)
-            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + startK, sm.bookK, escK, sm.w + sub * WROW * G, hi, lo);
+            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + startK, sm.bookK, escK, sm.w + sub * 2 * WROW * G, hi, lo);
 #endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
             k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km, t, b, h);
@@ -525,7 +538,7 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okV[sub];
 #if !(KVC_DEBUG_SKIP & 2)
-            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + startV, sm.bookV, escV, sm.ps + grp * WROW * G, hi, lo);
+            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + startV, sm.bookV, escV, sm.ps + grp * 2 * WROW * G, hi, lo);
 #endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
 #pragma unroll

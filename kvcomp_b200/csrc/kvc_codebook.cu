@@ -150,14 +150,14 @@ __device__ void build_trees(BookSmem &s) {
     s.n_nodes = n;
 }
 
-// Decode table entry for a KVC_LUT_BITS-bit window w (first stream bit = MSB), 8 bytes:
-//   x  up to four complete symbols found in the window, one byte each, unused bytes 0
-//   y  how far the decoder state advances: (symbols << 16) | bits consumed   (0 = escape)
-// The decoder state is (position in the vector << 16) | bit offset, so one add applies an entry.
+// Decode table entry for a KVC_LUT_BITS-bit window w (first stream bit = MSB), 32 bits:
+//   byte 0      how far the decoder state advances: (symbols << 6) | bits consumed   (0 = escape)
+//   bytes 1..3  up to three complete symbols found in the window, unused bytes 0
+// The decoder state is (position in the vector << 6) | bit offset, so one add applies an entry.
 // When no code completes inside the window (a code longer than the window, or no code at all)
-// y is 0 and x holds the wide-tree node the window's bits lead to; the slow path continues from
-// there one bit at a time.
-__device__ uint2 lut_entry(const uint32_t *tree, uint32_t w) {
+// byte 0 is 0 and the upper bytes hold the wide-tree node the window's bits lead to; the slow path
+// continues from there one bit at a time.
+__device__ uint32_t lut_entry(const uint32_t *tree, uint32_t w) {
     uint32_t syms = 0, nsym = 0, used = 0;
     int idx = -1, pos = 0;
     while (pos < KVC_LUT_BITS) {
@@ -169,11 +169,11 @@ __device__ uint2 lut_entry(const uint32_t *tree, uint32_t w) {
         if ((tree[idx] & 0xffffu) == KVC_TREE_LEAF) {
             syms |= (tree[idx] >> 16) << (8 * nsym);
             nsym++; used = pos; idx = -1;
-            if (nsym == 4) break;
+            if (nsym == 3) break;
         }
     }
-    if (nsym) return make_uint2(syms, (nsym << 16) | used);
-    return make_uint2(idx < 0 ? (uint32_t)KVC_TREE_NONE : (uint32_t)idx, 0u);
+    if (nsym) return (syms << 8) | (nsym << 6) | used;
+    return (idx < 0 ? (uint32_t)KVC_TREE_NONE : (uint32_t)idx) << 8;
 }
 
 __device__ void write_book(const BookSmem &s, uint8_t *book, int tid, int nthr) {
@@ -197,7 +197,7 @@ __device__ void write_book(const BookSmem &s, uint8_t *book, int tid, int nthr) 
     }
     uint32_t *wt = reinterpret_cast<uint32_t *>(book + KVC_BOOK_OFF_TREE);
     for (int i = tid; i < 512; i += nthr) wt[i] = s.tree[i];
-    uint2 *lut = reinterpret_cast<uint2 *>(book + KVC_BOOK_OFF_LUT);
+    uint32_t *lut = reinterpret_cast<uint32_t *>(book + KVC_BOOK_OFF_LUT);
     for (int w = tid; w < KVC_LUT_SIZE; w += nthr) lut[w] = lut_entry(s.tree, (uint32_t)w);
     if (tid == 0) {
         kvc_book_header *h = reinterpret_cast<kvc_book_header *>(book);

@@ -4,7 +4,7 @@
 // A vector is 128 symbols, MSB-first, starting on a byte boundary (kernels.cu:237-291 walks it
 // one bit at a time through a tree in global memory).  Here the block's bytes sit in shared
 // memory, the thread keeps 64 bits of the stream in two registers and looks up KVC_LUT_BITS
-// bits at a time in a shared-memory table that returns up to four symbols per lookup; codes
+// bits at a time in a shared-memory table that returns up to three symbols per lookup; codes
 // longer than the window continue bit by bit from the tree node the window leads to.
 #pragma once
 
@@ -12,7 +12,7 @@
 
 struct KvcBookSmem {                      // per-CTA copy of the decode structures of one book
     uint32_t tree[512];
-    uint2 lut[KVC_LUT_SIZE];
+    uint32_t lut[KVC_LUT_SIZE];
 };
 
 __device__ __forceinline__ void kvc_load_book(KvcBookSmem &b, const void *book, int tid, int nthr) {
@@ -98,11 +98,12 @@ __device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
 
 // Decode one vector.  slot_s: shared-space address of the staged block (16-byte aligned); byte_pos:
 // where the vector starts in it; lut_s / tree_s: shared-space addresses of the book's tables.
-// The decoder state is (position << 16) | bit offset into the (hi, lo) register pair, so applying a
-// table entry is one add and (state >> 13) is position * 8 whatever the bit offset is.
-// emit(syms, c8): `syms` holds up to four symbols, one per byte, for positions c..c+3 of the vector
-// (unused bytes are 0), c8 = c * 8 (the byte offset of an 8-byte weight record).  At the very end of
-// a vector it may be handed symbols for positions beyond 127; the consumer keeps room for them.
+// The decoder state is (position << 6) | bit offset into the (hi, lo) register pair, so applying a
+// table entry is one add of its low byte.
+// emit(syms, c4): `syms` holds up to three symbols in bytes 0..2 for positions c..c+2 of the vector
+// (unused bytes are 0, byte 3 is 0), c4 = c * 4 (the byte offset of a 4-byte weight word).  At the
+// very end of a vector it may be handed symbols for positions beyond 127; the consumer keeps room
+// for them.
 // ESC = false is for books whose longest code fits the table window: no escape test in the loop.
 // Every round advances by at least one symbol, so the loop ends after at most 128 rounds; a corrupt
 // stream can read at most a few hundred bytes past its vector, for which the kernels keep padding
@@ -118,14 +119,15 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
     bool ok = true;
     do {
         const uint32_t win = __funnelshift_l(lo, hi, state);          // the shift uses the low 5 bits
-        const uint2 e = kvc_lds64(lut_s + ((win >> (32 - KVC_LUT_BITS - 3)) & ((KVC_LUT_SIZE - 1) << 3)));
-        if (!ESC || e.y != 0) {
-            emit(e.x, state >> 13);
-            state += e.y;
+        const uint32_t e = kvc_lds32(lut_s + ((win >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
+        const uint32_t adv = e & 0xffu;
+        if (!ESC || adv != 0) {
+            emit(e >> 8, (state >> 4) & 0x3fcu);                      // bit offset < 64: (c << 6) >> 4 = c * 4
+            state += adv;
         } else {                                                      // code longer than the window
-            uint32_t node = e.x, sym = 0;
+            uint32_t node = e >> 8, sym = 0;
             bool found = false;
-            const uint32_t c8 = state >> 13;
+            const uint32_t c4 = (state >> 4) & 0x3fcu;
             state += KVC_LUT_BITS;
             for (int guard = 0; guard < 40; guard++) {
                 if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
@@ -137,10 +139,10 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
                 node = (nd >> (16 * bit)) & 0xffffu;
             }
             ok = ok && found;
-            emit(sym, c8);
-            state += 1u << 16;
+            emit(sym, c4);
+            state += 1u << 6;
         }
         if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
-    } while (state < (KVC_VEC_LEN << 16));
+    } while (state < (KVC_VEC_LEN << 6));
     return ok;
 }

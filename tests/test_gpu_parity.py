@@ -238,11 +238,12 @@ def test_long_codes_use_the_slow_path(ops):
     """A very skewed alphabet has codes longer than the decode window; the stream still round-trips."""
     rng = np.random.default_rng(1)
     p = np.array([2.0 ** -(i + 1) for i in range(20)]); p[-1] = p[-2]; p /= p.sum()
+    p[12:] = p[12:].sum() / 8                       # keep the long codes frequent enough to occur often
     codes = rng.choice(20, size=(128, 1, 2, 128), p=p).astype(np.uint8)
     codes[5, 0, 1, :20] = np.arange(20)          # make sure every symbol occurs
     for is_k in (True, False):
         book = ops.build_codebook(ops.histogram(dev(codes)))
-        assert book.header()["max_len"] > 11
+        assert book.header()["max_len"] > 12
         bi = torch.zeros(8 * 4, dtype=torch.uint8, device="cuda")
         ti = torch.zeros(64 * 4, dtype=torch.int16, device="cuda")
         enc = torch.zeros(codes.size, dtype=torch.uint8, device="cuda")
