@@ -1,0 +1,142 @@
+"""KVCompCache: the KV-cache object the patched model files construct and call
+(models/cache/kvcomp_cache.py:22-38, models/cache/kvcomp_quant.py:14-123; call sites
+models/llama.py:279-283,848-852, models/mistral.py:168-171,840-844, models/phi3.py:197-201,916-920).
+
+    cache = KVCompCache(batch_size, head_num, head_dim, layer_num)
+    k, v = cache.update(key_states, value_states, layer_idx, {"cos": cos, "sin": sin})   # drop-in
+    out = cache.attend(query_states, layer_idx, scaling)                                 # fused path
+
+`update` keeps the reference's contract: RoPE is applied to the new keys inside, the tokens are
+appended, and the whole cache comes back as fp16 [B, H, T, D] for eager attention -- compressed
+blocks dequantised (what the reference's simulated path returns, kvcomp_quant.py:70-75), recent
+tokens as they are.  `append` + `attend` is the path that never materialises K/V: the tokens go into
+the compressed store and one kernel computes softmax(q K^T * scaling) V straight from the streams.
+"""
+import inspect
+import math
+
+import torch
+
+from .. import ops
+from .._lib import KvcError
+from ..utils.compute import apply_rotary_pos_emb_single, safe_cat
+from ..utils.config import KVCompCacheConfigStatic
+from .kvcomp_encode import KVCompCtx
+
+try:                                    # transformers 4.50's Cache takes no constructor arguments
+    from transformers import Cache as _HFCache
+    _BASE = _HFCache if not [p for p in list(inspect.signature(_HFCache.__init__).parameters.values())[1:]
+                             if p.default is inspect.Parameter.empty and p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)] else object
+except Exception:                       # pragma: no cover
+    _BASE = object
+
+
+class KVCompCache(_BASE):
+    def __init__(self, batch_size, head_num, head_dim, layer_num):
+        if _BASE is not object:
+            try:
+                super().__init__()
+            except Exception:
+                pass
+        if KVCompCacheConfigStatic.config is None:
+            raise ValueError("KVCompCacheConfigStatic.config is not set. Please set it before using KVCompCache.")
+        self.batch_size, self.head_num, self.head_dim, self.layer_num = batch_size, head_num, head_dim, layer_num
+        self.k_ctx = [None] * layer_num       # created at the first update: the KV head count is only known then
+        self.v_ctx = [None] * layer_num
+        self.k_plain = [None] * layer_num     # enable_quant = False: plain fp16 concatenation [B, H, T, D]
+        self.v_plain = [None] * layer_num
+        self.coss = [None] * layer_num
+        self.sins = [None] * layer_num
+        self._ws = {}
+
+    # ---- appending --------------------------------------------------------------------------------
+    def _ctx(self, layer_idx, kv_heads):
+        cfg = KVCompCacheConfigStatic.config
+        if self.k_ctx[layer_idx] is None:
+            self.k_ctx[layer_idx] = KVCompCtx(True, self.batch_size, kv_heads, self.head_dim, cfg.k_quant_scale_rel)
+            self.v_ctx[layer_idx] = KVCompCtx(False, self.batch_size, kv_heads, self.head_dim, cfg.v_quant_scale_rel)
+        return self.k_ctx[layer_idx], self.v_ctx[layer_idx]
+
+    def append(self, key_states, value_states, layer_idx, cache_kwargs=None):
+        """Add new tokens (key/value_states: [B, Hkv, t, D]); keys get RoPE here unless pre-RoPE is on."""
+        cfg = KVCompCacheConfigStatic.config
+        cos, sin = cache_kwargs["cos"], cache_kwargs["sin"]
+        if cfg.enable_pre_rope:
+            self.coss[layer_idx] = safe_cat(self.coss[layer_idx], cos, dim=1)
+            self.sins[layer_idx] = safe_cat(self.sins[layer_idx], sin, dim=1)
+        else:
+            key_states = apply_rotary_pos_emb_single(key_states, cos, sin)
+        if not cfg.enable_quant:
+            self.k_plain[layer_idx] = safe_cat(self.k_plain[layer_idx], key_states, dim=2)
+            self.v_plain[layer_idx] = safe_cat(self.v_plain[layer_idx], value_states, dim=2)
+            return
+        kc, vc = self._ctx(layer_idx, key_states.shape[1])
+        kc.store(key_states.permute(2, 0, 1, 3).contiguous().half())
+        vc.store(value_states.permute(2, 0, 1, 3).contiguous().half())
+
+    def update(self, key_states, value_states, layer_idx, cache_kwargs=None):
+        """The reference's Cache.update: append, then return the whole K and V as [B, Hkv, T, D]."""
+        cfg = KVCompCacheConfigStatic.config
+        self.append(key_states, value_states, layer_idx, cache_kwargs)
+        if not cfg.enable_quant:
+            k, v = self.k_plain[layer_idx], self.v_plain[layer_idx]
+        else:
+            k = self.k_ctx[layer_idx].get()[0].permute(1, 2, 0, 3)
+            v = self.v_ctx[layer_idx].get()[0].permute(1, 2, 0, 3)
+        if cfg.enable_pre_rope:
+            k = apply_rotary_pos_emb_single(k, self.coss[layer_idx], self.sins[layer_idx])
+        return k, v
+
+    def get_seq_length(self, layer_idx=0):
+        layer_idx = 0 if layer_idx is None else layer_idx
+        if not KVCompCacheConfigStatic.config.enable_quant:
+            return 0 if self.k_plain[layer_idx] is None else self.k_plain[layer_idx].shape[2]
+        return 0 if self.k_ctx[layer_idx] is None else self.k_ctx[layer_idx].ctx_len
+
+    # ---- fused decode attention -------------------------------------------------------------------
+    def _tails(self, kc, vc):
+        """Compressed length the fused kernel reads and the fp16 tails that follow it.  K and V cut
+        their recent windows with different block and window sizes, so one of them may have a few more
+        compressed tokens than the other; those are dequantised into the tail."""
+        T = min(kc.compressed_ctx_len, vc.compressed_ctx_len) // 128 * 128
+        tails = []
+        for c in (kc, vc):
+            parts = []
+            if c.compressed_ctx_len > T:
+                x, _ = c.get_only_compressed()
+                parts.append(x[T:])
+            if c.buffer is not None and c.buffer.shape[0]:
+                parts.append(c.buffer)
+            tails.append(torch.cat(parts, dim=0).contiguous() if parts else None)
+        return T, tails[0], tails[1]
+
+    def attend(self, query_states, layer_idx, scaling=None):
+        """One decode step: query_states [B, Hq, 1, D] (or [B, Hq, D]), already rotated -> attention
+        output of the same shape, computed straight from the compressed K and V of the layer."""
+        cfg = KVCompCacheConfigStatic.config
+        if not cfg.enable_quant or cfg.enable_pre_rope:
+            raise KvcError("attend needs enable_quant and post-RoPE keys; use update() otherwise")
+        kc, vc = self.k_ctx[layer_idx], self.v_ctx[layer_idx]
+        if kc is None:
+            raise KvcError("attend before any update")
+        q = query_states
+        squeeze = q.dim() == 4
+        if squeeze:
+            if q.shape[2] != 1:
+                raise KvcError("attend handles one query token (decode); use update() for prefill")
+            q = q[:, :, 0, :]
+        q = q.contiguous().half()
+        B, Hq, D = q.shape
+        scaling = 1.0 / math.sqrt(D) if scaling is None else scaling
+        T, ktail, vtail = self._tails(kc, vc)
+        if T == 0 and ktail is None:
+            raise KvcError("empty cache")
+        if T == 0:      # nothing compressed yet: the kernel only walks the fp16 rows, but still wants streams
+            raise KvcError("attend needs at least 128 compressed tokens; use update() while the cache is shorter")
+        splits = ops.attn_splits(T, B, kc.head_num)
+        key = (q.device, B, Hq, splits)
+        if key not in self._ws:
+            self._ws[key] = ops.attn_workspace(B, Hq, splits, q.device)
+        out, st = ops.attn_decode(kc.cache(), vc.cache(), T, B, kc.head_num, q, scaling, ktail, vtail,
+                                  splits=splits, workspace=self._ws[key])
+        return out.unsqueeze(2) if squeeze else out

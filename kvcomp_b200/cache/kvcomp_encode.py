@@ -1,0 +1,270 @@
+"""KVCompCtx: the compressed store of one layer's K or V (models/cache/kvcomp_encode.py:15-326).
+
+Same constructor, methods and bookkeeping as the reference class, with the work moved into the CUDA
+library: the quantiser is one kernel instead of ~8 torch ops, histogram and codebook are built on the
+device, and the stream grows inside pre-reserved arenas instead of torch.cat on every store
+(kvcomp_encode.py:129-133).  Beyond the reference: ChannelQuant / VectorQuant for K, per-sequence
+units, any batch size in the fused kernels, and `cache()` for the one-pass decode attention.
+"""
+from math import gcd
+
+import torch
+
+from .. import ops
+from .._lib import KvcError
+from ..utils.compute import QuantMode, cut_tensor_ctx_len_0
+from ..utils.config import KVCompCacheConfigStatic
+
+_MODE = {QuantMode.BlockQuant: ops.MODE_BLOCK, QuantMode.ChannelQuant: ops.MODE_CHANNEL,
+         QuantMode.TokenQuant: ops.MODE_TOKEN, QuantMode.VectorQuant: ops.MODE_VECTOR}
+
+
+class _Arena:
+    """A 1-D device buffer that grows geometrically; `n` elements are in use."""
+
+    def __init__(self, dtype):
+        self.dtype, self.buf, self.n = dtype, None, 0
+
+    def reserve(self, extra, device):
+        need = self.n + extra
+        if self.buf is None or self.buf.numel() < need:
+            cap = max(need, int((self.buf.numel() if self.buf is not None else 0) * 1.5), 1024)
+            new = torch.empty(cap, dtype=self.dtype, device=device)
+            if self.buf is not None and self.n:
+                new[:self.n] = self.buf[:self.n]
+            self.buf = new
+        return self.buf[self.n:need]
+
+    def used(self):
+        return self.buf[:self.n] if self.buf is not None else None
+
+
+class KVCompCtx:
+    def __init__(self, is_k, batch_size, head_num, head_dim, quant_scale_rel,
+                 encode_codebook_path=None, decode_codebook_path=None):
+        cfg = KVCompCacheConfigStatic.config
+        assert cfg is not None, "KVCompCacheConfigStatic.config is None"
+        assert head_dim == 128, "head_dim must be equal to K_VEC_LEN and V_VEC_LEN for cuda kernel implementation"
+        self.is_k = is_k
+        self.batch_size, self.head_num, self.head_dim = batch_size, head_num, head_dim
+        self.quant_scale_rel = quant_scale_rel
+        self.quant_mode = cfg.k_quant_mode if is_k else cfg.v_quant_mode
+        self.block_size = cfg.k_block_size if is_k else cfg.v_block_size
+        self.recent_size = cfg.k_recent_size if is_k else cfg.v_recent_size
+        self.batch_shared = not getattr(cfg, "quant_per_sequence", False)
+        self.min_dtype = torch.int16 if getattr(cfg, "wide_min_ints", False) else torch.int8
+        if is_k:
+            assert self.block_size % 64 == 0, "for K, block size must be divisible by VEC_PER_BLK"
+            assert self.quant_mode in _MODE
+            self.cut_block = self.block_size
+        else:
+            assert self.quant_mode in (QuantMode.TokenQuant, QuantMode.VectorQuant, QuantMode.BlockQuant), \
+                "V units must not depend on the channel"
+            self.cut_block = self.block_size * 128 // gcd(self.block_size, 128)     # whole 128-token vectors
+        self.spec = ops.qspec(_MODE[self.quant_mode], self.batch_shared, batch_size, head_num, head_dim,
+                              self.block_size)
+        self.ctx_len = 0
+        self.compressed_ctx_len = 0
+        self.device = None
+        self.buffer = None                       # uncompressed recent tokens, fp16 [r, B, H, D]
+        self.book = None
+        self.max_block_bytes = 0
+        self._enc = _Arena(torch.uint8)
+        self._bi = _Arena(torch.uint8)
+        self._ti = _Arena(torch.int16)
+        self._mi = _Arena(self.min_dtype)
+        self._sc = _Arena(torch.float16)
+        self._hist = None
+
+    # ---- views with the reference's attribute names --------------------------------------------
+    @property
+    def encoded_data(self):
+        return self._enc.used()
+
+    @property
+    def block_infos(self):
+        return self._bi.used()
+
+    @property
+    def thread_infos(self):
+        u = self._ti.used()
+        return None if u is None else u.view(torch.uint8)
+
+    def _unit_shape(self):
+        s = self.spec
+        B, H, D = self.batch_size, self.head_num, self.head_dim
+        nb = 1 if (s.sb == 0) else B
+        nh = 1 if (s.sh == 0) else H
+        nc = 1 if (s.sc == 0) else D
+        per_blk = self.block_size // s.tok_div if s.tok_div <= self.block_size else 1
+        return (-1, per_blk, nb, nh, nc)
+
+    @property
+    def quant_min_ints(self):
+        u = self._mi.used()
+        return None if u is None else u.view(*self._unit_shape())
+
+    @property
+    def quant_scales(self):
+        u = self._sc.used()
+        return None if u is None else u.view(*self._unit_shape())
+
+    @property
+    def encode_codebook(self):
+        return None if self.book is None else self.book.encode_table()
+
+    @property
+    def decode_codebook(self):
+        return None if self.book is None else self.book.ref_decode_tensor().to(self.device)
+
+    @property
+    def shape(self):
+        return torch.Size([self.compressed_ctx_len, self.batch_size, self.head_num, self.head_dim])
+
+    # ---- store ------------------------------------------------------------------------------------
+    def _check(self, cache):
+        assert cache.dtype == torch.float16, "cache must be float16"
+        assert cache.shape[1] == self.batch_size, "batch size mismatch"
+        assert cache.shape[2] == self.head_num, "head num mismatch"
+        assert cache.shape[3] == self.head_dim, "head dim mismatch"
+        if self.device is None:
+            self.device = cache.device
+        assert self.device == cache.device, "device mismatch"
+
+    def _quantize(self, x, hist):
+        T = x.shape[0]
+        n = self.spec.units(T, self.batch_size, self.head_num, self.head_dim)
+        mi = self._mi.reserve(n, self.device)
+        sc = self._sc.reserve(n, self.device)
+        codes, _, _, _, st = ops.quantize(x, _MODE[self.quant_mode], self.block_size, self.quant_scale_rel,
+                                          self.batch_shared, min_dtype=self.min_dtype, hist=hist, min_int=mi, scale=sc)
+        return codes, n, st
+
+    def store(self, cache):
+        """Append tokens [t, B, H, D]; whole blocks beyond the recent window are quantised and encoded.
+        Returns the uint8 codes of the newly compressed tokens as [n_blocks, block, B, H, D] (or None)."""
+        self._check(cache)
+        self.ctx_len += cache.shape[0]
+        to_compress, self.buffer = cut_tensor_ctx_len_0(self.buffer, cache, self.cut_block, self.recent_size)
+        if to_compress is None:
+            return None
+        x = to_compress.contiguous()
+        T = x.shape[0]
+        hist = None
+        if self.book is None:
+            hist = torch.zeros(256, dtype=torch.int64, device=self.device)
+        codes, n_units, st_q = self._quantize(x, hist)
+        if self.book is None:
+            self.book = ops.build_codebook(hist)
+        cols = self.batch_size * self.head_num
+        bsz, tsz, _, cap = ops.buffer_sizes(T, cols * self.head_dim, self.is_k)
+        bi = self._bi.reserve(bsz, self.device)
+        ti = self._ti.reserve(tsz // 2, self.device)
+        enc = self._enc.reserve(cap, self.device)                  # the reference reserves numel bytes too
+        total = torch.tensor([0, self.max_block_bytes], dtype=torch.int64, device=self.device)
+        total, st_e = ops.encode(codes, self.is_k, self.book.encode_table(), bi, ti, enc,
+                                 base_offset=self._enc.n, total=total)
+        n_bytes, max_block = (int(v) for v in total.tolist())      # synchronises, as the reference does
+        ops.read_status(st_q, what="quantize")
+        ops.read_status(st_e, what="entropy_encode")
+        self._enc.n += n_bytes
+        self._bi.n += bsz
+        self._ti.n += tsz // 2
+        self._mi.n += n_units
+        self._sc.n += n_units
+        self.max_block_bytes = max_block
+        self.compressed_ctx_len += T
+        return codes.view(-1, self.block_size, self.batch_size, self.head_num, self.head_dim)
+
+    def build_codebook(self, tensors):
+        """Freeze the codebook from sample tensors before the first store (kvcomp_encode.py:282-306)."""
+        assert len(tensors) > 0, "tensors must not be empty"
+        hist = None
+        for cache in tensors:
+            self._check(cache)
+            blocked = cache.shape[0] // self.block_size * self.block_size
+            if blocked == 0:
+                continue
+            x = cache[:blocked].contiguous()
+            if hist is None:
+                hist = torch.zeros(256, dtype=torch.int64, device=self.device)
+            mi = torch.empty(self.spec.units(blocked, self.batch_size, self.head_num, self.head_dim),
+                             dtype=self.min_dtype, device=self.device)
+            ops.quantize(x, _MODE[self.quant_mode], self.block_size, self.quant_scale_rel, self.batch_shared,
+                         min_dtype=self.min_dtype, hist=hist, min_int=mi)
+        if hist is None:
+            raise KvcError("build_codebook: no whole block in the sample tensors")
+        self.book = ops.build_codebook(hist)
+        hd = self.book.header()
+        assert hd["min_sym"] == 0, "shift must be 0"
+
+    # ---- read back --------------------------------------------------------------------------------
+    def _require(self):
+        assert self.compressed_ctx_len > 0 and self.book is not None, "nothing has been compressed yet"
+
+    def get_decode_quant_ints(self):
+        """Decoded uint8 codes [n_blocks, block, B, H, D] and the kernel time in ms."""
+        self._require()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out, st = ops.decode(self._enc.used(), self._bi.used(), self._ti.used(), self.book,
+                             self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k)
+        stop.record()
+        stop.synchronize()
+        ops.read_status(st, what="entropy_decode")
+        return out.view(-1, self.block_size, self.batch_size, self.head_num, self.head_dim), start.elapsed_time(stop)
+
+    def get_only_compressed(self):
+        """Dequantised compressed part [T, B, H, D] and the time of decode + dequantisation in ms."""
+        codes, t = self.get_decode_quant_ints()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        x = ops.dequant(codes.view(self.compressed_ctx_len, self.batch_size, self.head_num, self.head_dim),
+                        self._mi.used(), self._sc.used(), self.spec)
+        stop.record()
+        stop.synchronize()
+        return x, t + start.elapsed_time(stop)
+
+    def get(self):
+        """Whole cache [ctx_len, B, H, D]: dequantised compressed part followed by the recent window."""
+        if self.compressed_ctx_len == 0:
+            return self.buffer, 0.0
+        x, t = self.get_only_compressed()
+        return (torch.cat([x, self.buffer], dim=0) if self.buffer is not None and self.buffer.shape[0] else x), t
+
+    def cache(self):
+        """The kvc_cache argument of the fused kernels (valid until the next store)."""
+        self._require()
+        return ops.make_cache(self._enc.buf, self._bi.buf, self._ti.buf, self.book, self._mi.buf, self._sc.buf,
+                              self.spec, self._enc.n, self.max_block_bytes)
+
+    def mat_vec_mul(self, B):
+        """K: scores [batch, heads, ctx] = q . K^T; V: [1, batch, heads, 128] = P . V over the compressed
+        tokens (kvcomp_encode.py:209-280).  Returns (tensor, ms)."""
+        self._require()
+        assert B.dtype == torch.float16, "B must be float16"
+        assert len(B.shape) == 3, "B must be 3D tensor"
+        assert B.shape[0] == self.batch_size, "batch size mismatch"
+        hq = B.shape[1]
+        assert hq % self.head_num == 0, "head num mismatch"
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if self.is_k:
+            assert B.shape[2] == self.head_dim, "head dim mismatch"
+            start.record()
+            C, st = ops.fused_qk(self.cache(), self.compressed_ctx_len, self.batch_size, self.head_num, B)
+        else:
+            assert B.shape[2] == self.compressed_ctx_len, "ctx len mismatch"
+            start.record()
+            part, st = ops.fused_pv(self.cache(), self.compressed_ctx_len, self.batch_size, self.head_num, B)
+            C = part.float().sum(dim=0, keepdim=True).half()
+        stop.record()
+        stop.synchronize()
+        ops.read_status(st, what="mat_vec_mul")
+        return C, start.elapsed_time(stop)
+
+    def get_cr(self):
+        """Compression ratio with the reference's accounting (kvcomp_encode.py:317-326)."""
+        compressed = (self._bi.n + self._ti.n * 2 + self._enc.n + self._mi.n * self._mi.used().element_size() +
+                      self._sc.n * 2)
+        original = 2 * self.batch_size * self.compressed_ctx_len * self.head_num * self.head_dim
+        return original / compressed

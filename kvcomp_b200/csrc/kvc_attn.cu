@@ -31,7 +31,7 @@ namespace {
 
 constexpr int SLOT_BYTES = 8192 + 32;     // a block is at most 8191 bytes (u16 fields) + alignment lead
 constexpr int SLOT_PAD = 1024;           // readable bytes behind the last staging slot
-constexpr int WROW = 132;                 // weight records per vector: 128 positions + zeroed overrun
+constexpr int WROW = 136;                 // weight words per vector: 128 positions + zeroed overrun (>= 128 + KVC_DECODE_OVERRUN + 1)
 constexpr int NTHR = 256;
 
 struct CacheDev {
@@ -153,40 +153,55 @@ __device__ __forceinline__ uint32_t vec_start(const uint16_t *thread_info, long 
 }
 
 // ---- K weights --------------------------------------------------------------------------------------
-// Weight records of the 4 blocks of a 256-token tile: w[sub][c][g], step[sub][g], zp[sub][g].
-// One warp per (block, query head): lane = 4 consecutive channels.
+// Weight words of the 4 blocks of a 256-token tile: w[sub][hi|lo][c][g], step[sub][g], zp[sub][g].
+// Warp `wp` owns block sub = wp & 3 and the query heads g = (wp >> 2) * GH .. + GH - 1 (GH = G/2, or
+// all of them on warps 0-3 when G = 1); lane = 4 consecutive channels.
 // Units that depend on the channel (sc != 0) need tok_div % 64 == 0 so that a block shares them;
 // otherwise scale and min_int are per-token scalars applied after the dot product (k_finish).
-template <int G>
-__device__ __forceinline__ void k_weights(uint32_t *w, float *step, float *zp, const float *qf, const kvc_qmeta_dev &m,
-                                          long long tok0, long long T, long long b, long long h, int tid) {
-    const int lane = tid & 31, warp = tid >> 5;
-    for (int pair = warp; pair < 4 * G; pair += NTHR / 32) {
-        const int sub = pair / G, g = pair - sub * G;
-        const long long t = tok0 + sub * 64;
-        float wv[4] = {0.f, 0.f, 0.f, 0.f}, z = 0.f;
-        if (t < T) {
-            const long long ub = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
+struct KUnit { float sc[4]; float ms[4]; };     // scale and min_int*scale of the lane's 4 channels
+
+// global -> registers; issued a tile ahead so that the latency hides behind the decode
+__device__ __forceinline__ void k_units_load(KUnit &u, const kvc_qmeta_dev &m, long long tok0, long long T,
+                                             long long b, long long h, int tid) {
+    const int lane = tid & 31, sub = (tid >> 5) & 3;
+    const long long t = tok0 + sub * 64;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int c = lane * 4 + i;
-                float q = qf[g * 128 + c];
-                if (m.sc != 0) {
-                    const long long u = ub + (long long)c * m.sc;
-                    const float sc = __half2float(m.scale[u]);
-                    z = fmaf((float)kvc_load_min(m, u) * sc, q, z);
-                    q *= sc;
-                }
-                wv[i] = q;
-            }
+    for (int i = 0; i < 4; i++) { u.sc[i] = 1.f; u.ms[i] = 0.f; }
+    if (m.sc != 0 && t < T) {
+        const long long ub = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const long long un = ub + (long long)(lane * 4 + i) * m.sc;
+            u.sc[i] = __half2float(m.scale[un]);
+            u.ms[i] = (float)kvc_load_min(m, un) * u.sc[i];
+        }
+    }
+}
+
+template <int G>
+__device__ __forceinline__ void k_weights_build(uint32_t *w, float *step, float *zp, const float *qf, const KUnit &u,
+                                                bool channel_units, long long tok0, long long T, int tid) {
+    const int lane = tid & 31, wp = tid >> 5, sub = wp & 3;
+    constexpr int GH = G >= 2 ? G / 2 : 1;
+    if (G == 1 && wp >= 4) return;
+    const bool live = tok0 + sub * 64 < T;
+#pragma unroll
+    for (int gi = 0; gi < GH; gi++) {
+        const int g = G == 1 ? 0 : (wp >> 2) * GH + gi;
+        float wv[4], z = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float q = live ? qf[g * 128 + lane * 4 + i] : 0.f;
+            wv[i] = q * u.sc[i];
+            z = fmaf(u.ms[i], q, z);
         }
         float mx = fmaxf(fmaxf(fabsf(wv[0]), fabsf(wv[1])), fmaxf(fabsf(wv[2]), fabsf(wv[3])));
         mx = kvc_warp_max(mx);
-        z = kvc_warp_sum(z);
-        const float st = fix_step(mx);
+        z = channel_units ? kvc_warp_sum(z) : 0.f;
+        const float st = fix_step(mx), inv = st > 0.f ? 1.0f / st : 0.f;
         int q4[7];
 #pragma unroll
-        for (int i = 0; i < 4; i++) q4[i] = fix_quant(wv[i], st);
+        for (int i = 0; i < 4; i++) q4[i] = __float2int_rn(wv[i] * inv);
 #pragma unroll
         for (int i = 0; i < 3; i++) {                           // the next lane's first three values
             int nv = __shfl_down_sync(0xffffffffu, q4[i], 1);
@@ -199,8 +214,16 @@ __device__ __forceinline__ void k_weights(uint32_t *w, float *step, float *zp, c
             row[(lane * 4 + i) * G + g] = r.x; row[WROW * G + (lane * 4 + i) * G + g] = r.y;
         }
         if (lane < WROW - 128) { row[(128 + lane) * G + g] = 0u; row[WROW * G + (128 + lane) * G + g] = 0u; }
-        if (lane == 0) { step[pair] = st; zp[pair] = z; }
+        if (lane == 0) { step[sub * G + g] = st; zp[sub * G + g] = z; }
     }
+}
+
+template <int G>
+__device__ __forceinline__ void k_weights(uint32_t *w, float *step, float *zp, const float *qf, const kvc_qmeta_dev &m,
+                                          long long tok0, long long T, long long b, long long h, int tid) {
+    KUnit u;
+    k_units_load(u, m, tok0, T, b, h, tid);
+    k_weights_build<G>(w, step, zp, qf, u, m.sc != 0, tok0, T, tid);
 }
 
 template <int G>
@@ -245,7 +268,7 @@ __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red
     const int lane = tid & 31, warp = tid >> 5, grp = tid >> 7, tl = tid & 127;
 #pragma unroll
     for (int g = 0; g < G; g++) { float mx = kvc_warp_max(fabsf(wv[g])); if (lane == 0) red[warp * G + g] = mx; }
-    if (tl < 4) for (int g = 0; g < G; g++) q16[(grp * G + g) * 132 + 128 + tl] = 0;
+    if (tl < 4) for (int g = 0; g < G; g++) q16[(grp * G + g) * 132 + 128 + tl] = 0;   // tl < 4
     __syncthreads();
 #pragma unroll
     for (int g = 0; g < G; g++) {
@@ -413,7 +436,7 @@ struct AttnParams {
 
 // BULK: stage with bulk asynchronous copies (one tile phase ahead) instead of plain loads.
 template <int G, bool BULK>
-__global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
+__global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     AttnSmem<G> &sm = *reinterpret_cast<AttnSmem<G> *>(smem_raw);
     uint8_t *const slotsK = smem_raw + sizeof(AttnSmem<G>), *const slotsV = slotsK + 4 * p.slotK_bytes;
@@ -452,13 +475,28 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
     float m_run[G], l_run[G], acc[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
-#ifdef KVC_DEBUG_DELAY
-    {
-        const unsigned lin = blockIdx.y * gridDim.x + blockIdx.x;
-        const unsigned slot = (lin / 148u) % 3u;
-        for (unsigned i = 0; i < slot * KVC_DEBUG_DELAY; i++) __nanosleep(1000);
-    }
-#endif
+
+    // Per-thread metadata of a tile (vector start offsets, the token's V scale / min_int, the K unit
+    // parameters of the warp's block) is fetched one tile ahead, so that no global-memory latency
+    // sits between the phases of a tile.
+    struct TileMeta { uint32_t startK, startV; float vsc, vmi; KUnit ku; };
+    auto load_meta = [&](long long tile, TileMeta &tm) {
+        const long long tok0 = tile * 256, t = tok0 + tid;
+        const long long gI = tok0 / 128 + grp;
+        tm.startK = tm.startV = 0u; tm.vsc = tm.vmi = 0.f;
+        if (tile < tile_hi) {
+            if (t < T) {
+                tm.startK = vec_start(p.k.thread_info, (tok0 / 64 + sub) * cols + col, v);
+                const long long u = (t / vm.tok_div) * vm.sj + b * vm.sb + h * vm.sh;
+                tm.vsc = __half2float(vm.scale[u]); tm.vmi = (float)kvc_load_min(vm, u);
+            }
+            if (gI * 128 < T) tm.startV = vec_start(p.v.thread_info, gI * (cols * 2) + col * 2 + (ch >> 6), v);
+        }
+        k_units_load(tm.ku, km, tile < tile_hi ? tok0 : T, T, b, h, tid);
+    };
+    TileMeta cur, nxt;
+    load_meta(tile_lo, cur);
+    __syncthreads();                                       // books, q and (unbuffered) slots are in place
 
     uint32_t phase = 0;
     for (long long tile = tile_lo; tile < tile_hi; tile++, phase ^= 1u) {
@@ -467,20 +505,12 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
         const long long gI = tok0 / 128 + grp;
         const long long blkV = gI * (cols * 2) + col * 2 + (ch >> 6);
         const bool actK = t < T, actV = gI * 128 < T;
-        __syncthreads();                                   // weights, reductions (and unbuffered slots) are free
-        // per-thread metadata of this tile, requested early so that the loads overlap the weight build
-        const uint32_t startK = actK ? vec_start(p.k.thread_info, blkK, v) : 0u;
-        const uint32_t startV = actV ? vec_start(p.v.thread_info, blkV, v) : 0u;
-        float vsc = 0.f, vmi = 0.f;
-        if (actK) {
-            const long long u = (t / vm.tok_div) * vm.sj + b * vm.sb + h * vm.sh;
-            vsc = __half2float(vm.scale[u]); vmi = (float)kvc_load_min(vm, u);
-        }
+        load_meta(tile + 1, nxt);
         if (!BULK) {
             if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
             if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
         }
-        k_weights<G>(sm.w, sm.kstep, sm.zp, sm.qf, km, tok0, T, b, h, tid);
+        k_weights_build<G>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, tok0, T, tid);
         if (BULK && !kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
         __syncthreads();
         // ---- K: scores of this tile's tokens
@@ -491,7 +521,7 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okK[sub];
 #if !(KVC_DEBUG_SKIP & 1)
-            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + startK, sm.bookK, escK, sm.w + sub * 2 * WROW * G, hi, lo);
+            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + cur.startK, sm.bookK, escK, sm.w + sub * 2 * WROW * G, hi, lo);
 #endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
             k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km, t, b, h);
@@ -515,8 +545,8 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
             alpha[g] = __expf(m_run[g] - m_new);           // exp(-inf) = 0 on the first tile
             const float pr = actK ? __expf(s[g] - m_new) : 0.f;
             m_run[g] = m_new;
-            wv[g] = pr * vsc;
-            const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * vmi);
+            wv[g] = pr * cur.vsc;
+            const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * cur.vmi);
             if (lane == 0) { sm.red[1][warp * G + g] = ssum; sm.red[2][warp * G + g] = zsum; }
         }
         v_weights<G>(sm.ps, sm.vstep, sm.red[3], sm.q16, wv, tid);      // three barriers inside
@@ -538,7 +568,7 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okV[sub];
 #if !(KVC_DEBUG_SKIP & 2)
-            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + startV, sm.bookV, escV, sm.ps + grp * 2 * WROW * G, hi, lo);
+            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + cur.startV, sm.bookV, escV, sm.ps + grp * 2 * WROW * G, hi, lo);
 #endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
 #pragma unroll
@@ -549,11 +579,10 @@ __global__ void __launch_bounds__(NTHR, 3) attn_decode_kernel(AttnParams p) {
         }
 #pragma unroll
         for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
-        if (BULK) {
-            __syncthreads();                               // every thread is done with the V slots
-            if (warp == 0)                                 // next tile's V blocks land during its K phase
-                stage_bulk(p.v, validV(tile + 1, lane & 3), blkV_of(tile + 1, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
-        }
+        __syncthreads();                                   // every thread is done with the V slots, weights and sums
+        if (BULK && warp == 0)                             // next tile's V blocks land during its K phase
+            stage_bulk(p.v, validV(tile + 1, lane & 3), blkV_of(tile + 1, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
+        cur = nxt;
     }
     if (BULK && tile_lo < tile_hi) {      // the copies issued for the tile after the last one are empty, but their phase must end
         if (!kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;

@@ -8,7 +8,7 @@
 namespace {
 
 constexpr int SLOT_BYTES = 8192 + 32;      // a block is at most 8191 bytes (u16 fields) + alignment lead
-constexpr int TILE_STRIDE = 132;
+constexpr int TILE_STRIDE = 136;          // 128 symbols + KVC_DECODE_OVERRUN + 2 of padding, a multiple of 4
 
 struct DecodeSmem {
     KvcBookSmem book;

@@ -10,6 +10,9 @@
 
 #include "kvc_common.cuh"
 
+#define KVC_DECODE_UNROLL 1
+#define KVC_DECODE_OVERRUN (3 * KVC_DECODE_UNROLL)   // positions past 127 a decoder may emit
+
 struct KvcBookSmem {                      // per-CTA copy of the decode structures of one book
     uint32_t tree[512];
     uint32_t lut[KVC_LUT_SIZE];
@@ -101,9 +104,9 @@ __device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
 // The decoder state is (position << 6) | bit offset into the (hi, lo) register pair, so applying a
 // table entry is one add of its low byte.
 // emit(syms, c4): `syms` holds up to three symbols in bytes 0..2 for positions c..c+2 of the vector
-// (unused bytes are 0, byte 3 is 0), c4 = c * 4 (the byte offset of a 4-byte weight word).  At the
-// very end of a vector it may be handed symbols for positions beyond 127; the consumer keeps room
-// for them.
+// (unused bytes are 0, byte 3 is 0), c4 = c * 4 (the byte offset of a 4-byte weight word).  The end
+// of the vector is tested once per KVC_DECODE_UNROLL lookups, so emit may be handed symbols for
+// positions up to 127 + KVC_DECODE_OVERRUN; the consumer keeps room for them (zero weights, padding).
 // ESC = false is for books whose longest code fits the table window: no escape test in the loop.
 // Every round advances by at least one symbol, so the loop ends after at most 128 rounds; a corrupt
 // stream can read at most a few hundred bytes past its vector, for which the kernels keep padding
@@ -118,6 +121,8 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
     ptr += 12;
     bool ok = true;
     do {
+#pragma unroll
+      for (int rep = 0; rep < KVC_DECODE_UNROLL; rep++) {             // the end test runs once per UNROLL lookups
         const uint32_t win = __funnelshift_l(lo, hi, state);          // the shift uses the low 5 bits
         const uint32_t e = kvc_lds32(lut_s + ((win >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
         const uint32_t adv = e & 0xffu;
@@ -143,6 +148,7 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
             state += 1u << 6;
         }
         if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
+      }
     } while (state < (KVC_VEC_LEN << 6));
     return ok;
 }
