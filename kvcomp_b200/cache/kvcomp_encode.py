@@ -146,6 +146,12 @@ class KVCompCtx:
         self._check(cache)
         self.ctx_len += cache.shape[0]
         to_compress, self.buffer = cut_tensor_ctx_len_0(self.buffer, cache, self.cut_block, self.recent_size)
+        if to_compress is not None and to_compress.shape[0] % self.cut_block:
+            # recent_size = 0 with a ragged length: the reference's slice clips to the length and its
+            # .view then fails (kvcomp_encode.py:83); here the ragged rest simply stays in the buffer
+            whole = to_compress.shape[0] // self.cut_block * self.cut_block
+            self.buffer = torch.cat([to_compress[whole:], self.buffer], dim=0)
+            to_compress = to_compress[:whole] if whole else None
         if to_compress is None:
             return None
         x = to_compress.contiguous()
@@ -156,6 +162,21 @@ class KVCompCtx:
         codes, n_units, st_q = self._quantize(x, hist)
         if self.book is None:
             self.book = ops.build_codebook(hist)
+        ops.read_status(st_q, what="quantize")
+        if not self._encode(codes):
+            # A symbol the frozen book has no code for.  The reference drops such symbols silently
+            # (kernels.cu:197-205: a table entry of length 0 adds no bits), which corrupts the stream.
+            # Here the book is rebuilt over everything stored so far plus every reachable code, and the
+            # cache is re-encoded once; this cannot happen again for this context.
+            self._rebook(codes)
+        self._mi.n += n_units
+        self._sc.n += n_units
+        self.compressed_ctx_len += T
+        return codes.view(-1, self.block_size, self.batch_size, self.head_num, self.head_dim)
+
+    def _encode(self, codes):
+        """Append the stream of `codes` [T, B, H, D] to the arenas.  False if the book lacks a symbol."""
+        T = codes.shape[0]
         cols = self.batch_size * self.head_num
         bsz, tsz, _, cap = ops.buffer_sizes(T, cols * self.head_dim, self.is_k)
         bi = self._bi.reserve(bsz, self.device)
@@ -165,16 +186,34 @@ class KVCompCtx:
         total, st_e = ops.encode(codes, self.is_k, self.book.encode_table(), bi, ti, enc,
                                  base_offset=self._enc.n, total=total)
         n_bytes, max_block = (int(v) for v in total.tolist())      # synchronises, as the reference does
-        ops.read_status(st_q, what="quantize")
+        flags = ops.read_status(st_e, raise_on_fatal=False)
+        if flags & ops._lib.FLAG_SYMBOL_MISSING:
+            return False
         ops.read_status(st_e, what="entropy_encode")
         self._enc.n += n_bytes
         self._bi.n += bsz
         self._ti.n += tsz // 2
-        self._mi.n += n_units
-        self._sc.n += n_units
         self.max_block_bytes = max_block
-        self.compressed_ctx_len += T
-        return codes.view(-1, self.block_size, self.batch_size, self.head_num, self.head_dim)
+        return True
+
+    def _rebook(self, new_codes):
+        old = None
+        if self.compressed_ctx_len:
+            old, st = ops.decode(self._enc.used(), self._bi.used(), self._ti.used(), self.book,
+                                 self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k)
+            ops.read_status(st, what="entropy_decode")
+        hist = ops.histogram(new_codes.view(-1))
+        if old is not None:
+            hist = ops.histogram(old.view(-1), hist)
+        reach = min(255, int(1.0 / self.quant_scale_rel) + 3)      # codes are 0 .. about 1/rel + 1
+        hist[:reach + 1] += 1
+        self.book = ops.build_codebook(hist)
+        self._enc.n = self._bi.n = self._ti.n = 0
+        self.max_block_bytes = 0
+        self.rebooks = getattr(self, "rebooks", 0) + 1
+        for part in (old, new_codes):
+            if part is not None and not self._encode(part):
+                raise KvcError("a code outside 0..%d appeared; the quantiser settings cannot produce it" % reach)
 
     def build_codebook(self, tensors):
         """Freeze the codebook from sample tensors before the first store (kvcomp_encode.py:282-306)."""
