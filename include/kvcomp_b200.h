@@ -200,6 +200,22 @@ int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B
                     void *out, int splits, void *workspace, int64_t workspace_bytes,
                     int32_t *status, kvc_stream_t stream);
 
+/* No counterpart in the reference.  kvc_attn_decode for callers that cannot allocate device memory
+ * (a serving process whose memory pool owns the whole device, a plugin under a fixed memory budget):
+ * the split-KV scratch is a fixed array inside the library (kvc_attn_static_capacity() bytes, 4 MiB,
+ * held by every GPU that loads the library until the process exits) instead of a caller workspace.
+ * Inputs and outputs are still the caller's.  Nothing is allocated or freed by this call.
+ *  - B, Hq and splits whose scratch (kvc_attn_workspace) exceeds the capacity: KVC_ERR_CAPACITY.
+ *  - The first call on a device looks the array's device address up (with that device current);
+ *    make that first call outside any stream capture.
+ *  - All calls on a device share the array: the counters are cleared on `stream` at the start of
+ *    every call, and two calls that overlap on the GPU (different streams) race.  Calls on one
+ *    stream are ordered and safe. */
+int64_t kvc_attn_static_capacity(void);
+int kvc_attn_decode_static(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t Hq,
+                           const void *q, float scaling, const void *ktail, const void *vtail, int64_t Tr,
+                           void *out, int splits, int32_t *status, kvc_stream_t stream);
+
 /* k_mat_vec_mul_cuda_export (kernels.cu:1192-1273): dense q.k over uncompressed fp16 K
  * [ctx,1,H,128], q [1,H,128] -> out fp16 [ctx,1,H].  Comparison baseline only. */
 int kvc_k_matvec(const void *k, const void *q, void *out, int64_t ctx, int64_t H, kvc_stream_t stream);

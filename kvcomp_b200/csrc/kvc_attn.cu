@@ -21,6 +21,8 @@
 // every decode: weight records are stored [position][G].
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "kvc_decode.cuh"
 
 #ifndef KVC_DEBUG_SKIP
@@ -859,4 +861,57 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     }
     KVC_LAUNCH_OK();
     return KVC_OK;
+}
+
+// ---- decode attention for callers that cannot allocate device memory ------------------------------
+// Some hosts of this library may not call cudaMalloc at all: an inference server whose memory pool
+// owns every byte of the device and forbids side allocations, a plugin loaded into a process that
+// runs under a fixed memory budget, or code that runs where an allocation would synchronise the
+// device at the wrong moment.  For them the split-KV scratch of the attention kernel (per-head
+// counters and the per-split partial results) lives in this fixed array instead of a workspace the
+// caller has to provide.  Every GPU that loads the library holds these bytes until the process exits.
+#define KVC_STATIC_SCRATCH_BYTES (4 << 20)
+static __device__ __align__(256) unsigned char g_attn_scratch[KVC_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+std::mutex g_scratch_mutex;
+void *g_scratch_ptr[MAX_DEVICES] = {};
+
+// The array's name is only a host-side handle in host code; the device address has to be asked for,
+// once per device, with that device current.
+int static_scratch(void **ptr) {
+    int dev = -1;
+    KVC_CUDA_OK(cudaGetDevice(&dev));
+    KVC_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "kvc_attn_decode_static: device %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_ptr[dev]) {
+        void *p = nullptr;
+        KVC_CUDA_OK(cudaGetSymbolAddress(&p, g_attn_scratch));
+        g_scratch_ptr[dev] = p;
+    }
+    *ptr = g_scratch_ptr[dev];
+    return KVC_OK;
+}
+}  // namespace
+
+extern "C" int64_t kvc_attn_static_capacity(void) { return KVC_STATIC_SCRATCH_BYTES; }
+
+extern "C" int kvc_attn_decode_static(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t Hq,
+                                      const void *q, float scaling, const void *ktail, const void *vtail, int64_t Tr,
+                                      void *out, int splits, int32_t *status, kvc_stream_t stream) {
+    KVC_REQUIRE(B > 0 && Hkv > 0 && Hq > 0 && T >= 0, "kvc_attn_decode_static: bad shape");
+    if (splits <= 0) splits = kvc_attn_splits(T, B, Hkv, 0);
+    const int64_t need = kvc_attn_workspace(B, Hq, splits);
+    if (need > KVC_STATIC_SCRATCH_BYTES) {
+        kvc_set_error("kvc_attn_decode_static: B=%lld x Hq=%lld x %d splits needs %lld bytes of scratch, the built-in "
+                      "array holds %d; lower `splits` or use kvc_attn_decode with a workspace",
+                      (long long)B, (long long)Hq, splits, (long long)need, KVC_STATIC_SCRATCH_BYTES);
+        return KVC_ERR_CAPACITY;
+    }
+    void *scratch = nullptr;
+    if (int rc = static_scratch(&scratch)) return rc;
+    // the array keeps whatever the previous call left: the per-head counters must start at zero
+    KVC_CUDA_OK(cudaMemsetAsync(scratch, 0, ((B * Hq * 4 + 255) / 256) * 256, kvc_cu(stream)));
+    return kvc_attn_decode(k, v, T, B, Hkv, Hq, q, scaling, ktail, vtail, Tr, out, splits, scratch, need, status, stream);
 }

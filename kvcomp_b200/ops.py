@@ -301,6 +301,27 @@ def attn_decode(kcache, vcache, T, B, Hkv, q, scaling, ktail=None, vtail=None, o
     return out, status
 
 
+def attn_decode_static(kcache, vcache, T, B, Hkv, q, scaling, out, ktail=None, vtail=None, splits=0, status=None):
+    """attn_decode for callers that must not allocate: the split-KV scratch is the library's built-in
+    array, `out` and `status` are the caller's tensors, and this wrapper creates no tensor either.
+    Calls that overlap on the GPU share the scratch and race; keep them on one stream."""
+    lib = _lib.load()
+    _cuda(q, torch.float16, "q")
+    _cuda(out, torch.float16, "out")
+    if status is None:
+        raise KvcError("attn_decode_static: pass a status tensor (ops.new_status) made beforehand")
+    Tr = 0
+    if ktail is not None and ktail.shape[0] > 0:
+        Tr = ktail.shape[0]
+    else:
+        ktail = vtail = None
+    with torch.cuda.device(q.device):
+        _lib.check(lib.kvc_attn_decode_static(C.byref(kcache), C.byref(vcache), T, B, Hkv, q.shape[1], _p(q),
+                                              float(scaling), _p(ktail), _p(vtail), Tr, _p(out), int(splits),
+                                              _p(status), _stream()), "kvc_attn_decode_static")
+    return out
+
+
 def k_matvec(k, q, out):
     lib = _lib.load()
     for t, n in ((k, "A"), (q, "B"), (out, "C")):
