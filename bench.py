@@ -140,6 +140,8 @@ def algorithmic_bytes(acct, cfg):
 def cpu_sample(cfg, seed, min_seconds=8.0):
     """The CPU restatement on a bounded sample: one sequence of one layer (all heads, full context):
     Huffman-decode both streams, then one decode-attention step.  Returns seconds per sample."""
+    # torch.distributed.run pins OMP_NUM_THREADS to 1; the CPU arm is meant to use every host core
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import torch
     from kvcomp_b200.synth import make_kv
     from oracle import kvc_oracle as orc
@@ -199,6 +201,9 @@ def main():
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
+                    help="N > 1: every rank owns its own batch of sequences (weak scaling, default) or the KV heads "
+                         "are split over the ranks and the outputs all-gathered once per step (strong scaling)")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     if args.layers:
@@ -224,6 +229,12 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     from kvcomp_b200 import ops
 
+    heads_mode = args.shard == "heads" and world > 1
+    Hq_total = cfg["Hq"]
+    if heads_mode:
+        from kvcomp_b200 import sharding
+        _, kvc, _, qc = sharding.shard_heads(cfg["Hkv"], cfg["Hq"], world, rank)
+        cfg["Hkv"], cfg["Hq"] = kvc, qc
     T, B, Hkv, Hq, L = cfg["T"], cfg["B"], cfg["Hkv"], cfg["Hq"], cfg["layers"]
     layers, accts = [], []
     for l in range(L):
@@ -234,13 +245,17 @@ def main():
     splits = args.splits or ops.attn_splits(T, B, Hkv)
     ws = ops.attn_workspace(B, Hq, splits, device)
     status = ops.new_status(device)
-    outs = [torch.empty((B, Hq, 128), dtype=torch.float16, device=device) for _ in range(L)]
+    out_all = torch.empty((L, B, Hq, 128), dtype=torch.float16, device=device)
+    outs = [out_all[i] for i in range(L)]
+    gather_buf = torch.empty((world, L, B, Hq, 128), dtype=torch.float16, device=device) if heads_mode else None
     scaling = 1.0 / math.sqrt(128)
     launches_per_call = sum(1 for _ in _chunks(Hq // Hkv))
 
     def step():
         for (caches, _, q), out in zip(layers, outs):
             ops.attn_decode(caches[0], caches[1], T, B, Hkv, q, scaling, out=out, splits=splits, workspace=ws, status=status)
+        if heads_mode:      # the only exchange of the path: the step's outputs of every rank's query heads
+            dist.all_gather_into_tensor(gather_buf, out_all)
 
     def barrier():
         torch.cuda.synchronize()
@@ -276,6 +291,8 @@ def main():
             q_dev[i].copy_(q_host[i], non_blocking=True)
             ops.attn_decode(caches[0], caches[1], T, B, Hkv, q_dev[i], scaling, out=out, splits=splits, workspace=ws, status=status)
             o_host[i].copy_(out, non_blocking=True)
+        if heads_mode:
+            dist.all_gather_into_tensor(gather_buf, out_all)
         torch.cuda.current_stream().synchronize()       # the caller needs the result of the step
 
     for _ in range(2):
@@ -300,8 +317,9 @@ def main():
         return
 
     ms_step = ms / args.steps
-    value = B * world / (ms_step / 1e3)
-    e2e_value = B * world / (ms_e2e / args.steps / 1e3)
+    seqs = B if heads_mode else B * world             # sequences the whole job advances by one token per step
+    value = seqs / (ms_step / 1e3)
+    e2e_value = seqs / (ms_e2e / args.steps / 1e3)
     alg = float(np.mean([algorithmic_bytes(a, cfg) for a in accts]))
     launch_s = ms_step / 1e3 / (L * launches_per_call)
     peak, peak_kind = peaks()
@@ -310,11 +328,12 @@ def main():
     line = {
         "metric": "decode attn tokens/s (fused decomp-matvec)", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u8 codes -> f32 accumulate, fp16 in/out", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong" if heads_mode else "weak", "vs_baseline": None,
+        "dtype": "u8 codes -> int32 dot products (16-bit fixed-point weights), f32 softmax, fp16 in/out", "data": "synthetic",
         "config": {"workload": args.workload + ": " + cfg["desc"], "layers": L, "splits": splits,
                    "l2": "inputs larger than L2 (%.2f GB of compressed cache read per step)" % (alg * L / 1e9),
-                   "sharding": "batch sequences per rank, no collective on the data path"},
+                   "sharding": ("KV heads split over ranks (%d of %d query heads each), one NCCL all-gather of the outputs per step" % (Hq, Hq_total))
+                   if heads_mode else "batch sequences per rank, no collective on the data path"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind + " (STREAM-style copy)", "traffic": None,
                      "algorithmic_bytes_per_launch": alg, "launch_ms": launch_s * 1e3,
