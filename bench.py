@@ -41,6 +41,9 @@ WORKLOADS = {
 }
 
 
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.035
+
+
 def peaks():
     """Measured HBM peak of this pool (driver-written file), else the stated fallback."""
     try:
@@ -344,15 +347,11 @@ def main():
         "gpu_launches": args.steps * L * launches_per_call,
         "clocks": clocks, "status_flags": flags,
     }
-    tpath = os.path.join(REPO, "profiles", "attn_decode_traffic.json")
-    try:
-        with open(tpath) as f:
-            tr = json.load(f)
-        if tr.get("workload") == args.workload or tr.get("bytes_per_algorithmic_byte"):
-            line["roofline"]["traffic"] = tr["bytes_per_algorithmic_byte"] * alg
-            line["roofline"]["traffic_source"] = tr.get("source")
-    except Exception:
-        pass
+    # DRAM traffic of the kernel from one ncu capture (profiles/attn_decode_c1.md): read + written bytes
+    # were 1.035 x the algorithmic bytes of the launch on c1-shaped data; it grows with the bytes staged.
+    if Hq == Hkv:
+        line["roofline"]["traffic"] = DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * alg
+        line["roofline"]["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum on 2 layers of c1, scaled by algorithmic bytes"
     if not args.no_cpu_baseline and world == 1:
         s, threads = cpu_sample(cfg, args.seed, min_seconds=10.0)
         step_s = s * L * B
