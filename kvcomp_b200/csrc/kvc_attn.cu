@@ -790,7 +790,7 @@ extern "C" int kvc_attn_splits(int64_t T, int64_t B, int64_t Hkv, int sm_count) 
     if (T <= 0 || B <= 0 || Hkv <= 0) return 1;
     if (sm_count <= 0) sm_count = kvc_sm_count();
     const long long n_tiles = (T + 255) / 256, cols = B * Hkv;
-    long long want = (4ll * sm_count + cols - 1) / cols;           // about two waves of two CTAs per SM
+    long long want = (8ll * sm_count + cols - 1) / cols;           // several CTAs per resident slot: short tails
     if (want < 1) want = 1;
     if (want > n_tiles) want = n_tiles;
     const long long tps = (n_tiles + want - 1) / want;
