@@ -301,6 +301,16 @@ class KVCompCtx:
         ops.read_status(st, what="mat_vec_mul")
         return C, start.elapsed_time(stop)
 
+    def save(self, path):
+        """Write this cache to a file (kvcomp_b200.cache.storage describes the format)."""
+        from .storage import save_ctx
+        return save_ctx(self, path)
+
+    @staticmethod
+    def load(path, device="cuda"):
+        from .storage import load_ctx
+        return load_ctx(path, device)
+
     def get_cr(self):
         """Compression ratio with the reference's accounting (kvcomp_encode.py:317-326)."""
         compressed = (self._bi.n + self._ti.n * 2 + self._enc.n + self._mi.n * self._mi.used().element_size() +

@@ -250,3 +250,47 @@ def test_cache_disabled_quant_is_plain_concat(cfg):
     cache = KVCompCache(B, H, 128, 1)
     K, V = cache.update(k, v, 0, {"cos": cos.cuda(), "sin": sin.cuda()})
     assert torch.equal(V, v) and K.shape == k.shape and cache.get_seq_length(0) == 10
+
+
+def test_ctx_save_load_roundtrip(cfg, tmp_path):
+    """A cache written to disk and read back decodes to the same codes, keeps its recent window and
+    accepts further stores."""
+    from kvcomp_b200.cache import KVCompCtx
+    cfg(kmode="ChannelQuant", krec=128, vrec=256, quant_per_sequence=True, wide_min_ints=True)
+    B, H = 2, 2
+    k, v, _ = synth(900, B, H, seed=12)
+    for is_k, x in ((True, k.cuda()), (False, v.cuda())):
+        ctx = KVCompCtx(is_k, B, H, 128, 0.05)
+        ctx.store(x[:700])
+        path = str(tmp_path / ("k.kvc" if is_k else "v.kvc"))
+        hdr = ctx.save(path)
+        assert hdr["compressed_ctx_len"] == ctx.compressed_ctx_len and "encoded" in hdr["sections"]
+        back = KVCompCtx.load(path)
+        assert back.compressed_ctx_len == ctx.compressed_ctx_len and back.ctx_len == 700
+        assert torch.equal(back.get_decode_quant_ints()[0], ctx.get_decode_quant_ints()[0])
+        assert torch.equal(back.get()[0], ctx.get()[0])
+        ctx.store(x[700:])
+        back.store(x[700:])
+        assert torch.equal(back.get()[0], ctx.get()[0]) and back.get_cr() == pytest.approx(ctx.get_cr())
+
+
+def test_evaluation_harness_keys(cfg):
+    """The evaluation entry point of evaluation/cr_throughput_eval.py:128-240: same result keys, one value
+    per layer, fused results within the reference's 1 % check."""
+    from kvcomp_b200.evaluation import crs_throughputs_evaluation_with_data, quant_rel_to_bit_num
+    c = cfg()
+    B, H, T, L = 1, 4, 512, 2
+    ks, vs = [], []
+    for l in range(L):
+        k, v, _ = synth(T, B, H, seed=40 + l)
+        ks.append(k.permute(1, 2, 0, 3).contiguous().cuda())
+        vs.append(v.permute(1, 2, 0, 3).contiguous().cuda())
+    r = crs_throughputs_evaluation_with_data(c, ks, vs)
+    for key in ("k_quant_crs", "v_quant_crs", "k_huffman_crs", "v_huffman_crs", "k_time_multi_kernels",
+                "v_time_multi_kernels", "k_pytorch_mat_vec_mul_times", "v_pytorch_mat_vec_mul_times",
+                "k_fused_mat_vec_mul_times", "v_fused_mat_vec_mul_times", "k_throughput_multi_kernels",
+                "k_throughput_fused_kernels", "v_throughput_multi_kernels", "v_throughput_fused_kernels"):
+        assert len(r[key]) == L, key
+    assert all(x > 1.0 for x in r["k_huffman_crs"] + r["v_huffman_crs"])
+    assert all(h > q * 0.9 for h, q in zip(r["k_huffman_crs"], r["k_quant_crs"]))
+    assert quant_rel_to_bit_num(0.05) == 5 and quant_rel_to_bit_num(0.1) == 4
