@@ -56,12 +56,13 @@ CacheDev to_dev(const kvc_cache &c) {
 }
 
 // ---- 16-bit fixed-point weight records -----------------------------------------------------------
-// per position c: a word of the hi bytes of w[c..c+3] and a word of their lo bytes (pack4 gives {hi, lo})
-__device__ __forceinline__ uint2 pack4(int q0, int q1, int q2, int q3) {
+// per position c: a word {0, hi(w[c]), hi(w[c+1]), hi(w[c+2])} and a word of the lo bytes laid out the
+// same way, so that a decode-table entry {advance, s0, s1, s2} multiplies them directly (the advance
+// byte meets the zero).  pack4 gives {hi word, lo word}; q3 is unused.
+__device__ __forceinline__ uint2 pack4(int q0, int q1, int q2, int /*q3*/) {
     uint2 r;
-    r.x = ((uint32_t)(q0 >> 8) & 0xffu) | (((uint32_t)(q1 >> 8) & 0xffu) << 8) |
-          (((uint32_t)(q2 >> 8) & 0xffu) << 16) | (((uint32_t)(q3 >> 8) & 0xffu) << 24);
-    r.y = ((uint32_t)q0 & 0xffu) | (((uint32_t)q1 & 0xffu) << 8) | (((uint32_t)q2 & 0xffu) << 16) | (((uint32_t)q3 & 0xffu) << 24);
+    r.x = (((uint32_t)(q0 >> 8) & 0xffu) << 8) | (((uint32_t)(q1 >> 8) & 0xffu) << 16) | (((uint32_t)(q2 >> 8) & 0xffu) << 24);
+    r.y = (((uint32_t)q0 & 0xffu) << 8) | (((uint32_t)q1 & 0xffu) << 16) | (((uint32_t)q2 & 0xffu) << 24);
     return r;
 }
 __device__ __forceinline__ float fix_step(float wmax) { return wmax > 0.f ? wmax * (1.0f / 32767.0f) : 0.f; }

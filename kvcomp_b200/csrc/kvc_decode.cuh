@@ -103,8 +103,9 @@ __device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
 // where the vector starts in it; lut_s / tree_s: shared-space addresses of the book's tables.
 // The decoder state is (position << 6) | bit offset into the (hi, lo) register pair, so applying a
 // table entry is one add of its low byte.
-// emit(syms, c4): `syms` holds up to three symbols in bytes 0..2 for positions c..c+2 of the vector
-// (unused bytes are 0, byte 3 is 0), c4 = c * 4 (the byte offset of a 4-byte weight word).  The end
+// emit(e, c4): `e` holds up to three symbols in bytes 1..3 for positions c..c+2 of the vector (unused
+// bytes are 0; byte 0 is the table entry's advance byte and must be ignored), c4 = c * 4 (the byte
+// offset of a 4-byte weight word).  The end
 // of the vector is tested once per KVC_DECODE_UNROLL lookups, so emit may be handed symbols for
 // positions up to 127 + KVC_DECODE_OVERRUN; the consumer keeps room for them (zero weights, padding).
 // ESC = false is for books whose longest code fits the table window: no escape test in the loop.
@@ -125,10 +126,9 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
       for (int rep = 0; rep < KVC_DECODE_UNROLL; rep++) {             // the end test runs once per UNROLL lookups
         const uint32_t win = __funnelshift_l(lo, hi, state);          // the shift uses the low 5 bits
         const uint32_t e = kvc_lds32(lut_s + ((win >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
-        const uint32_t adv = e & 0xffu;
-        if (!ESC || adv != 0) {
-            emit(e >> 8, (state >> 4) & 0x3fcu);                      // bit offset < 64: (c << 6) >> 4 = c * 4
-            state += adv;
+        if (!ESC || (e & 0xffu) != 0) {
+            emit(e, (state >> 4) & 0x3fcu);                           // bit offset < 64: (c << 6) >> 4 = c * 4
+            state = (uint32_t)kvc_dp4a_uu(e, 1u, (int)state);         // state += byte 0 of e, off the integer ALU pipe
         } else {                                                      // code longer than the window
             uint32_t node = e >> 8, sym = 0;
             bool found = false;
@@ -144,7 +144,7 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
                 node = (nd >> (16 * bit)) & 0xffffu;
             }
             ok = ok && found;
-            emit(sym, c4);
+            emit(sym << 8, c4);
             state += 1u << 6;
         }
         if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }

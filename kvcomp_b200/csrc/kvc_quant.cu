@@ -8,15 +8,16 @@
 
 namespace {
 
-struct UnitParam { float sf; float mi; };   // scale as float, min_int as float
+struct UnitParam { float sf; float mi; float rcp; };   // scale, min_int and 1/scale as floats
 
 __device__ __forceinline__ UnitParam unit_param(float mn, float mx, float rel, __half *scale_out, int *flags) {
     __half range = __float2half_rn(__fsub_rn(mx, mn));
     __half sc = __float2half_rn(__fmul_rn(__half2float(range), rel));
     UnitParam p;
     p.sf = __half2float(sc);
+    p.rcp = 0.0f;
     if (p.sf == 0.0f || p.sf != p.sf) { p.mi = 0.0f; *flags |= KVC_FLAG_ZERO_SCALE; }
-    else p.mi = rintf(__half2float(__float2half_rn(__fdiv_rn(mn, p.sf))));
+    else { p.mi = rintf(__half2float(__float2half_rn(__fdiv_rn(mn, p.sf)))); p.rcp = __frcp_rn(p.sf); }
     *scale_out = sc;
     return p;
 }
@@ -32,9 +33,16 @@ __device__ __forceinline__ void store_min(void *min_int, int min_bytes, long lon
     }
 }
 
+// fp16(x / scale) without the full IEEE division: q1 = x*r corrected once by the exact residual is within
+// 2^-24 (relative) of the true quotient t.  x and scale carry 11 significant bits, so t is at least
+// 2^-23 (relative) away from every midpoint between two fp16 values (t = m would need m*scale = x with a
+// 12-bit m); hence q1, the correctly rounded fp32 quotient and t all round to the same fp16 value.
 __device__ __forceinline__ uint32_t quant_one(__half x, const UnitParam &p, int *flags) {
     if (p.sf == 0.0f || p.sf != p.sf) return 0u;
-    float q = rintf(__half2float(__float2half_rn(__fdiv_rn(__half2float(x), p.sf))));
+    const float xf = __half2float(x);
+    const float q0 = __fmul_rn(xf, p.rcp);
+    const float q1 = __fmaf_rn(__fmaf_rn(-q0, p.sf, xf), p.rcp, q0);
+    float q = rintf(__half2float(__float2half_rn(q1)));
     float c = __half2float(__float2half_rn(__fsub_rn(q, p.mi)));
     if (!(c >= 0.0f && c <= 255.0f)) { *flags |= KVC_FLAG_CODE_OVERFLOW; }
     return (uint32_t)(int)c & 0xffu;
@@ -229,6 +237,7 @@ __global__ void __launch_bounds__(256) quant_block_apply_kernel(
     if (ghist) { for (int i = tid; i < 256; i += 256) shist[i] = 0; __syncthreads(); }
     UnitParam p;
     p.sf = __uint_as_float(ws[2 * u]); p.mi = __uint_as_float(ws[2 * u + 1]);
+    p.rcp = (p.sf == 0.0f || p.sf != p.sf) ? 0.0f : __frcp_rn(p.sf);
     int flags = 0;
     for (long long k = tid; k < row_len / 8; k += 256) {
         uint4 v = *reinterpret_cast<const uint4 *>(x + row * row_len + k * 8);
