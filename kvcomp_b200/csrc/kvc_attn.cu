@@ -154,6 +154,12 @@ __device__ __forceinline__ void stage_bulk(const CacheDev &kc, bool valid, long 
 __device__ __forceinline__ uint32_t vec_start(const uint16_t *thread_info, long long blk, int v) {
     return v ? (uint32_t)(thread_info[blk * 64 + v - 1] >> 3) : 0u;
 }
+// the same in two steps: the load (issued a tile ahead) and the shift (at the use)
+__device__ __forceinline__ unsigned short vec_start_bits(const uint16_t *thread_info, long long blk, int v) {
+    unsigned short r = 0;
+    if (v) r = thread_info[blk * 64 + v - 1];
+    return r;
+}
 
 // ---- K weights --------------------------------------------------------------------------------------
 // Weight words of the 4 blocks of a 256-token tile: w[sub][hi|lo][c][g], step[sub][g], zp[sub][g].
@@ -161,7 +167,7 @@ __device__ __forceinline__ uint32_t vec_start(const uint16_t *thread_info, long 
 // all of them on warps 0-3 when G = 1); lane = 4 consecutive channels.
 // Units that depend on the channel (sc != 0) need tok_div % 64 == 0 so that a block shares them;
 // otherwise scale and min_int are per-token scalars applied after the dot product (k_finish).
-struct KUnit { float sc[4]; float ms[4]; };     // scale and min_int*scale of the lane's 4 channels
+struct KUnit { unsigned short sc[4]; short mi[4]; };     // scale (fp16 bits) and min_int of the lane's 4 channels
 
 // global -> registers; issued a tile ahead so that the latency hides behind the decode
 __device__ __forceinline__ void k_units_load(KUnit &u, const kvc_qmeta_dev &m, long long tok0, long long T,
@@ -169,14 +175,14 @@ __device__ __forceinline__ void k_units_load(KUnit &u, const kvc_qmeta_dev &m, l
     const int lane = tid & 31, sub = (tid >> 5) & 3;
     const long long t = tok0 + sub * 64;
 #pragma unroll
-    for (int i = 0; i < 4; i++) { u.sc[i] = 1.f; u.ms[i] = 0.f; }
+    for (int i = 0; i < 4; i++) { u.sc[i] = 0x3c00; u.mi[i] = 0; }          // 1.0, 0
     if (m.sc != 0 && t < T) {
-        const long long ub = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
+        const long long ub = kvc_tok_unit(t, m.tok_div) * m.sj + b * m.sb + h * m.sh;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const long long un = ub + (long long)(lane * 4 + i) * m.sc;
-            u.sc[i] = __half2float(m.scale[un]);
-            u.ms[i] = (float)kvc_load_min(m, un) * u.sc[i];
+            u.sc[i] = kvc_load_scale_bits(m, un);
+            u.mi[i] = (short)kvc_load_min(m, un);
         }
     }
 }
@@ -195,8 +201,9 @@ __device__ __forceinline__ void k_weights_build(uint32_t *w, float *step, float 
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const float q = live ? qf[g * 128 + lane * 4 + i] : 0.f;
-            wv[i] = q * u.sc[i];
-            z = fmaf(u.ms[i], q, z);
+            const float sc = kvc_scale_value(u.sc[i]);
+            wv[i] = q * sc;
+            z = fmaf((float)u.mi[i] * sc, q, z);
         }
         float mx = fmaxf(fmaxf(fabsf(wv[0]), fabsf(wv[1])), fmaxf(fabsf(wv[2]), fabsf(wv[3])));
         mx = kvc_warp_max(mx);
@@ -245,19 +252,21 @@ __device__ __forceinline__ void load_q(float *qf, float *qsum, const __half *q, 
     }
 }
 
+// scale and min_int of a token whose K units do not depend on the channel (loaded ahead of the decode)
+__device__ __forceinline__ void k_token_unit(unsigned short &sc, int &mi, const kvc_qmeta_dev &m, long long t,
+                                             long long b, long long h) {
+    const long long u = kvc_tok_unit(t, m.tok_div) * m.sj + b * m.sb + h * m.sh;
+    sc = kvc_load_scale_bits(m, u); mi = kvc_load_min(m, u);
+}
+
 // score of the thread's token from its integer dot products
 template <int G>
 __device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], const int (&lo)[G], const float *step_sub,
-                                         const float *zp_sub, const float *qsum, const kvc_qmeta_dev &m,
-                                         long long t, long long b, long long h) {
-    if (m.sc != 0) {
+                                         const float *zp_sub, const float *qsum, bool channel_units, float sc, float mi) {
 #pragma unroll
-        for (int g = 0; g < G; g++) s[g] = fix_value(step_sub[g], hi[g], lo[g]) + zp_sub[g];
-    } else {
-        const long long u = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
-        const float sc = __half2float(m.scale[u]), mi = (float)kvc_load_min(m, u);
-#pragma unroll
-        for (int g = 0; g < G; g++) s[g] = sc * fmaf(mi, qsum[g], fix_value(step_sub[g], hi[g], lo[g]));
+    for (int g = 0; g < G; g++) {
+        const float d = fix_value(step_sub[g], hi[g], lo[g]);
+        s[g] = channel_units ? d + zp_sub[g] : sc * fmaf(mi, qsum[g], d);
     }
 }
 
@@ -327,6 +336,8 @@ __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T
     k_weights<G>(sm.w, sm.step, sm.zp, sm.qf, kc.q, tok0, T, b, h, tid);
     __syncthreads();
     if (!active) return;
+    unsigned short ksc = 0x3c00; int kmi = 0;
+    if (kc.q.sc == 0) k_token_unit(ksc, kmi, kc.q, t, b, h);
     int hi[G], lo[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
@@ -334,7 +345,7 @@ __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T
     if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(kc.thread_info, blk, v), sm.book, esc, sm.w + sub * 2 * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
     float s[G];
-    k_finish<G>(s, hi, lo, sm.step + sub * G, sm.zp + sub * G, sm.qsum, kc.q, t, b, h);
+    k_finish<G>(s, hi, lo, sm.step + sub * G, sm.zp + sub * G, sm.qsum, kc.q.sc != 0, kvc_scale_value(ksc), (float)kmi);
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const long long o = (b * Hq + hq0 + g) * T + t;
@@ -379,7 +390,7 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
     {
         float sc = 0.f, mi = 0.f;
         if (t < T) {
-            const long long u = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
+            const long long u = kvc_tok_unit(t, m.tok_div) * m.sj + b * m.sb + h * m.sh;
             sc = __half2float(m.scale[u]); mi = (float)kvc_load_min(m, u);
         }
 #pragma unroll
@@ -482,18 +493,19 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     // Per-thread metadata of a tile (vector start offsets, the token's V scale / min_int, the K unit
     // parameters of the warp's block) is fetched one tile ahead, so that no global-memory latency
     // sits between the phases of a tile.
-    struct TileMeta { uint32_t startK, startV; float vsc, vmi; KUnit ku; };
+    struct TileMeta { unsigned short startK, startV, vsc, ksc; int vmi, kmi; KUnit ku; };   // as loaded: no arithmetic waits on them here
     auto load_meta = [&](long long tile, TileMeta &tm) {
         const long long tok0 = tile * 256, t = tok0 + tid;
         const long long gI = tok0 / 128 + grp;
-        tm.startK = tm.startV = 0u; tm.vsc = tm.vmi = 0.f;
+        tm.startK = tm.startV = 0; tm.vsc = 0; tm.vmi = tm.kmi = 0; tm.ksc = 0x3c00;
         if (tile < tile_hi) {
             if (t < T) {
-                tm.startK = vec_start(p.k.thread_info, (tok0 / 64 + sub) * cols + col, v);
-                const long long u = (t / vm.tok_div) * vm.sj + b * vm.sb + h * vm.sh;
-                tm.vsc = __half2float(vm.scale[u]); tm.vmi = (float)kvc_load_min(vm, u);
+                tm.startK = vec_start_bits(p.k.thread_info, (tok0 / 64 + sub) * cols + col, v);
+                const long long u = kvc_tok_unit(t, vm.tok_div) * vm.sj + b * vm.sb + h * vm.sh;
+                tm.vsc = kvc_load_scale_bits(vm, u); tm.vmi = kvc_load_min(vm, u);
+                if (km.sc == 0) k_token_unit(tm.ksc, tm.kmi, km, t, b, h);
             }
-            if (gI * 128 < T) tm.startV = vec_start(p.v.thread_info, gI * (cols * 2) + col * 2 + (ch >> 6), v);
+            if (gI * 128 < T) tm.startV = vec_start_bits(p.v.thread_info, gI * (cols * 2) + col * 2 + (ch >> 6), v);
         }
         k_units_load(tm.ku, km, tile < tile_hi ? tok0 : T, T, b, h, tid);
     };
@@ -508,11 +520,18 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         const long long gI = tok0 / 128 + grp;
         const long long blkV = gI * (cols * 2) + col * 2 + (ch >> 6);
         const bool actK = t < T, actV = gI * 128 < T;
+#if KVC_DEBUG_SKIP & 16
+        nxt = cur;
+#else
         load_meta(tile + 1, nxt);
+#endif
         if (!BULK) {
             if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
             if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
         }
+#if KVC_DEBUG_SKIP & 4
+        if (tile == tile_lo)
+#endif
         k_weights_build<G>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, tok0, T, tid);
         if (BULK && !kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
         __syncthreads();
@@ -524,10 +543,10 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okK[sub];
 #if !(KVC_DEBUG_SKIP & 1)
-            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + cur.startK, sm.bookK, escK, sm.w + sub * 2 * WROW * G, hi, lo);
+            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, sm.w + sub * 2 * WROW * G, hi, lo);
 #endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
-            k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km, t, b, h);
+            k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km.sc != 0, kvc_scale_value(cur.ksc), (float)cur.kmi);
         } else {
 #pragma unroll
             for (int g = 0; g < G; g++) s[g] = -CUDART_INF_F;
@@ -548,10 +567,13 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             alpha[g] = __expf(m_run[g] - m_new);           // exp(-inf) = 0 on the first tile
             const float pr = actK ? __expf(s[g] - m_new) : 0.f;
             m_run[g] = m_new;
-            wv[g] = pr * cur.vsc;
-            const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * cur.vmi);
+            wv[g] = pr * kvc_scale_value(cur.vsc);
+            const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * (float)cur.vmi);
             if (lane == 0) { sm.red[1][warp * G + g] = ssum; sm.red[2][warp * G + g] = zsum; }
         }
+#if KVC_DEBUG_SKIP & 8
+        if (tile == tile_lo)
+#endif
         v_weights<G>(sm.ps, sm.vstep, sm.red[3], sm.q16, wv, tid);      // three barriers inside
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -571,7 +593,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okV[sub];
 #if !(KVC_DEBUG_SKIP & 2)
-            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + cur.startV, sm.bookV, escV, sm.ps + grp * 2 * WROW * G, hi, lo);
+            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, sm.ps + grp * 2 * WROW * G, hi, lo);
 #endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
 #pragma unroll

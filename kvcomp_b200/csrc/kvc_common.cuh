@@ -57,10 +57,23 @@ static inline kvc_qmeta_dev kvc_to_dev(const kvc_qmeta &q) {
     return d;
 }
 
-__device__ __forceinline__ int kvc_load_min(const kvc_qmeta_dev &m, long long u) {
-    return m.min_bytes == 1 ? (int)reinterpret_cast<const int8_t *>(m.min_int)[u]
-                            : (int)reinterpret_cast<const int16_t *>(m.min_int)[u];
+// t / tok_div without the emulated 64-bit division: token indices fit 32 bits in every real cache
+__device__ __forceinline__ long long kvc_tok_unit(long long t, int tok_div) {
+    if (tok_div == 1) return t;
+    if ((unsigned long long)t <= 0xffffffffull) return (long long)((uint32_t)t / (uint32_t)tok_div);
+    return t / tok_div;
 }
+
+__device__ __forceinline__ int kvc_load_min(const kvc_qmeta_dev &m, long long u) {
+    int r;                      // one sign-extending load either way: nothing consumes the value here
+    if (m.min_bytes == 1) r = reinterpret_cast<const int8_t *>(m.min_int)[u];
+    else r = reinterpret_cast<const int16_t *>(m.min_int)[u];
+    return r;
+}
+__device__ __forceinline__ unsigned short kvc_load_scale_bits(const kvc_qmeta_dev &m, long long u) {
+    return reinterpret_cast<const unsigned short *>(m.scale)[u];
+}
+__device__ __forceinline__ float kvc_scale_value(unsigned short bits) { return __half2float(__ushort_as_half(bits)); }
 
 __device__ __forceinline__ uint32_t kvc_bswap(uint32_t x) { return __byte_perm(x, 0, 0x0123); }
 

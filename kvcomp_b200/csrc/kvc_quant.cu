@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
     if (i >= rows * per_row) return;
     const long long row = i / per_row; const int c0 = (int)(i % per_row) * 8;
     const long long h = row % H, b = (row / H) % B, t = row / (H * B);
-    const long long ub = (t / m.tok_div) * m.sj + b * m.sb + h * m.sh;
+    const long long ub = kvc_tok_unit(t, m.tok_div) * m.sj + b * m.sb + h * m.sh;
     uint2 cv = *reinterpret_cast<const uint2 *>(codes + row * D + c0);
     const uint8_t *cb = reinterpret_cast<const uint8_t *>(&cv);
     uint4 o; __half *oh = reinterpret_cast<__half *>(&o);
