@@ -190,9 +190,14 @@ int kvc_fused_pv(const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t 
  * compressed caches: out[b,hq,:] = softmax(q K^T * scaling) V over T compressed tokens
  * plus Tr uncompressed tail tokens (the recent window, ktail/vtail device fp16
  * [Tr,B,Hkv,128], may be NULL with Tr = 0).  q: device fp16 [B,Hq,128]; out: device fp16
- * [B,Hq,128].  Scores never leave the SM; no fp16 K/V is written to memory.  splits = 0
- * picks a split count; workspace: kvc_attn_workspace() bytes of device memory, zeroed
- * once by the caller before the first use (the kernel leaves it zeroed). */
+ * [B,Hq,128].  Scores never leave the SM; no fp16 K/V is written to memory.
+ * Work is cut into items, one (sequence, KV head) column x one of `splits` equal runs of
+ * 256-token tiles; as many CTAs as the device holds at once take items until none is left,
+ * and a second small kernel merges the `splits` partial results of every head.  splits = 0
+ * picks kvc_attn_splits(T, B, Hkv, 0).  workspace: kvc_attn_workspace(B, Hq, splits) bytes
+ * of device memory whose first 256 bytes the caller zeroes once before the first use (the
+ * kernel leaves them zeroed); NULL is allowed when splits = 1.  Launches that share a
+ * workspace must not overlap on the device. */
 int64_t kvc_attn_workspace(int64_t B, int64_t Hq, int splits);
 int kvc_attn_splits(int64_t T, int64_t B, int64_t Hkv, int sm_count);
 int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t Hq,

@@ -133,10 +133,10 @@ class KVCompCache(_BASE):
             raise KvcError("empty cache")
         if T == 0:      # nothing compressed yet: the kernel only walks the fp16 rows, but still wants streams
             raise KvcError("attend needs at least 128 compressed tokens; use update() while the cache is shorter")
-        splits = ops.attn_splits(T, B, kc.head_num)
-        key = (q.device, B, Hq, splits)
+        parts = ops.attn_splits(T, B, kc.head_num)          # partial results per head of the balanced split
+        key = (q.device, B, Hq, parts)
         if key not in self._ws:
-            self._ws[key] = ops.attn_workspace(B, Hq, splits, q.device)
+            self._ws[key] = ops.attn_workspace(B, Hq, parts, q.device)
         out, st = ops.attn_decode(kc.cache(), vc.cache(), T, B, kc.head_num, q, scaling, ktail, vtail,
-                                  splits=splits, workspace=self._ws[key])
+                                  splits=0, workspace=self._ws[key])
         return out.unsqueeze(2) if squeeze else out

@@ -432,7 +432,7 @@ struct alignas(16) AttnSmem {                     // followed in shared memory b
     uint64_t bar[2];                  // K and V staging barriers
     uint32_t leadK[4], leadV[4];
     int okK[4], okV[4];
-    int last;
+    int next_j;                       // item the CTA drew for after the current one
 };
 
 struct AttnParams {
@@ -441,10 +441,12 @@ struct AttnParams {
     const __half *q, *ktail, *vtail;
     __half *out;
     float scaling;
-    int splits, tiles_per_split;
+    int n_tiles;                  // 256-token tiles per column
+    int splits, tiles_per_split;  // every column is cut into `splits` runs of `tiles_per_split` tiles
+    long long work;               // columns * splits items
     uint32_t slotK_bytes, slotV_bytes;   // capacity of one staging slot (multiple of 16)
     float *ws_part;               // [B*Hq][splits][130]: m, l, acc[128]
-    int *ws_count;                // [B*Hq]
+    int *sched;                   // {items handed out, CTAs finished}, or null: static shares
     int *status;
 };
 
@@ -457,81 +459,103 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
     const int grp = tid >> 7, ch = tid & 127;
     const long long T = p.T, B = p.B, Hkv = p.Hkv, Hq = p.Hq;
-    const long long cols = B * Hkv, col = blockIdx.y, b = col / Hkv, h = col % Hkv;
-    const long long Gt = Hq / Hkv, hq0 = h * Gt + p.g0;
-    const int split = blockIdx.x;
-    const long long n_tiles = (T + 255) / 256;
-    const long long tile_lo = (long long)split * p.tiles_per_split;
-    long long tile_hi = tile_lo + p.tiles_per_split;
-    if (tile_hi > n_tiles) tile_hi = n_tiles;
+    const long long cols = B * Hkv, Gt = Hq / Hkv;
+    const int n_tiles = p.n_tiles;
     const kvc_qmeta_dev &km = p.k.q, &vm = p.v.q;
     int flags = 0;
 
-    // block ids of the tile's four K blocks / four V blocks for lane l < 4 of the issuing warp
-    auto blkK_of = [&](long long tile, int l) { return ((tile * 256) / 64 + l) * cols + col; };
-    auto blkV_of = [&](long long tile, int l) { return ((tile * 256) / 128 + (l >> 1)) * (cols * 2) + col * 2 + (l & 1); };
-    auto validK = [&](long long tile, int l) { return tile < tile_hi && tile * 256 + l * 64 < T; };
-    auto validV = [&](long long tile, int l) { return tile < tile_hi && tile * 256 + (l >> 1) * 128 < T; };
+    // The work is cut into items: a column (one sequence, one KV head) x one of `splits` runs of
+    // `tiles_per_split` tiles; item j = column * splits + run.  Without a scheduling counter CTA i of P
+    // takes the items [work*i/P, work*(i+1)/P).  With one it takes items i and P + i and draws every
+    // further item from the counter, two items ahead of its use so that the answer has an item's time
+    // to arrive: CTAs that run faster (the warp schedulers favour some of an SM's CTAs) take more.
+    struct Item { int col, t_lo, t_hi; };
+    const bool draw = p.sched != nullptr;
+    const long long P = gridDim.x;
+    const long long w_hi = draw ? p.work : p.work * (blockIdx.x + 1) / P;
+    auto item_of = [&](long long j, Item &it) -> bool {
+        if (j >= w_hi) return false;
+        const int s = (int)(j % p.splits);
+        it.col = (int)(j / p.splits); it.t_lo = s * p.tiles_per_split; it.t_hi = min(n_tiles, it.t_lo + p.tiles_per_split);
+        return true;
+    };
+
+    // block ids of a tile's four K blocks / four V blocks for lane l < 4 of the issuing warp
+    auto blkK_of = [&](int col, int tile, int l) { return ((long long)tile * 4 + l) * cols + col; };
+    auto blkV_of = [&](int col, int tile, int l) { return ((long long)tile * 2 + (l >> 1)) * (cols * 2) + (long long)col * 2 + (l & 1); };
+    auto validK = [&](bool on, int tile, int l) { return on && (long long)tile * 256 + l * 64 < T; };
+    auto validV = [&](bool on, int tile, int l) { return on && (long long)tile * 256 + (l >> 1) * 128 < T; };
+
+    Item it, nit;
+    long long j_it = draw ? (long long)blockIdx.x : p.work * blockIdx.x / P, j_n1 = draw ? P + blockIdx.x : j_it + 1;
+    bool have = item_of(j_it, it), have_next = have && item_of(j_n1, nit);
+    int drawn = 0;                                         // thread 0: the counter's answer, used an item later
+    const bool any_tiles = have && it.t_lo < it.t_hi;      // items are empty only when the cache has no compressed part
 
     if (BULK) {
         if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); }
         __syncthreads();
-        if (warp == 0 && tile_lo < tile_hi) {
-            stage_bulk(p.k, validK(tile_lo, lane & 3), blkK_of(tile_lo, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
-            stage_bulk(p.v, validV(tile_lo, lane & 3), blkV_of(tile_lo, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
+        if (warp == 0 && any_tiles) {
+            stage_bulk(p.k, validK(true, it.t_lo, lane & 3), blkK_of(it.col, it.t_lo, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
+            stage_bulk(p.v, validV(true, it.t_lo, lane & 3), blkV_of(it.col, it.t_lo, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
         }
     }
     kvc_load_book(sm.bookK, p.k.book, tid, NTHR);
     kvc_load_book(sm.bookV, p.v.book, tid, NTHR);
     const bool escK = book_has_long_codes(p.k.book), escV = book_has_long_codes(p.v.book);
-    load_q<G>(sm.qf, sm.qsum, p.q, b, Hq, hq0, p.scaling, tid);
-
-    float m_run[G], l_run[G], acc[G];
-#pragma unroll
-    for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
 
     // Per-thread metadata of a tile (vector start offsets, the token's V scale / min_int, the K unit
     // parameters of the warp's block) is fetched one tile ahead, so that no global-memory latency
     // sits between the phases of a tile.
     struct TileMeta { unsigned short startK, startV, vsc, ksc; int vmi, kmi; KUnit ku; };   // as loaded: no arithmetic waits on them here
-    auto load_meta = [&](long long tile, TileMeta &tm) {
-        const long long tok0 = tile * 256, t = tok0 + tid;
+    auto load_meta = [&](bool on, int col, int tile, TileMeta &tm) {
+        const long long tok0 = (long long)tile * 256, t = tok0 + tid;
         const long long gI = tok0 / 128 + grp;
+        const int b = col / (int)Hkv, h = col % (int)Hkv;
         tm.startK = tm.startV = 0; tm.vsc = 0; tm.vmi = tm.kmi = 0; tm.ksc = 0x3c00;
-        if (tile < tile_hi) {
+        if (on) {
             if (t < T) {
                 tm.startK = vec_start_bits(p.k.thread_info, (tok0 / 64 + sub) * cols + col, v);
                 const long long u = kvc_tok_unit(t, vm.tok_div) * vm.sj + b * vm.sb + h * vm.sh;
                 tm.vsc = kvc_load_scale_bits(vm, u); tm.vmi = kvc_load_min(vm, u);
                 if (km.sc == 0) k_token_unit(tm.ksc, tm.kmi, km, t, b, h);
             }
-            if (gI * 128 < T) tm.startV = vec_start_bits(p.v.thread_info, gI * (cols * 2) + col * 2 + (ch >> 6), v);
+            if (gI * 128 < T) tm.startV = vec_start_bits(p.v.thread_info, gI * (cols * 2) + (long long)col * 2 + (ch >> 6), v);
         }
-        k_units_load(tm.ku, km, tile < tile_hi ? tok0 : T, T, b, h, tid);
+        k_units_load(tm.ku, km, on ? tok0 : T, T, b, h, tid);
     };
     TileMeta cur, nxt;
-    load_meta(tile_lo, cur);
-    __syncthreads();                                       // books, q and (unbuffered) slots are in place
+    load_meta(any_tiles, have ? it.col : 0, have ? it.t_lo : 0, cur);
 
     uint32_t phase = 0;
-    for (long long tile = tile_lo; tile < tile_hi; tile++, phase ^= 1u) {
-        const long long tok0 = tile * 256, t = tok0 + tid;
+    while (have) {
+    const int col = it.col, b = col / (int)Hkv, h = col % (int)Hkv;
+    const long long hq0 = h * Gt + p.g0;
+    if (draw && tid == 0) drawn = atomicAdd(&p.sched[0], 1);
+    load_q<G>(sm.qf, sm.qsum, p.q, b, Hq, hq0, p.scaling, tid);
+    __syncthreads();                                       // books, q and (unbuffered) slots are in place
+    float m_run[G], l_run[G], acc[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
+
+    for (int tile = it.t_lo; tile < it.t_hi; tile++, phase ^= 1u) {
+        const long long tok0 = (long long)tile * 256, t = tok0 + tid;
         const long long blkK = (tok0 / 64 + sub) * cols + col;
         const long long gI = tok0 / 128 + grp;
-        const long long blkV = gI * (cols * 2) + col * 2 + (ch >> 6);
+        const long long blkV = gI * (cols * 2) + (long long)col * 2 + (ch >> 6);
         const bool actK = t < T, actV = gI * 128 < T;
+        // the tile after this one in the CTA's sequence (it may open the next column)
+        bool n_on = true; int n_col = col, n_tile = tile + 1;
+        if (n_tile >= it.t_hi) { n_on = have_next && nit.t_lo < nit.t_hi; n_col = n_on ? nit.col : col; n_tile = n_on ? nit.t_lo : 0; }
 #if KVC_DEBUG_SKIP & 16
         nxt = cur;
 #else
-        load_meta(tile + 1, nxt);
+        load_meta(n_on, n_col, n_tile, nxt);
 #endif
         if (!BULK) {
             if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
             if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
         }
-#if KVC_DEBUG_SKIP & 4
-        if (tile == tile_lo)
-#endif
         k_weights_build<G>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, tok0, T, tid);
         if (BULK && !kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
         __syncthreads();
@@ -556,7 +580,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         for (int g = 0; g < G; g++) { float mx = kvc_warp_max(s[g]); if (lane == 0) sm.red[0][warp * G + g] = mx; }
         __syncthreads();                                   // also: every thread is done with the K slots
         if (BULK && warp == 0)                             // next tile's K blocks land during the V phase
-            stage_bulk(p.k, validK(tile + 1, lane & 3), blkK_of(tile + 1, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
+            stage_bulk(p.k, validK(n_on, n_tile, lane & 3), blkK_of(n_col, n_tile, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
         float alpha[G], wv[G];
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -571,9 +595,6 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * (float)cur.vmi);
             if (lane == 0) { sm.red[1][warp * G + g] = ssum; sm.red[2][warp * G + g] = zsum; }
         }
-#if KVC_DEBUG_SKIP & 8
-        if (tile == tile_lo)
-#endif
         v_weights<G>(sm.ps, sm.vstep, sm.red[3], sm.q16, wv, tid);      // three barriers inside
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -606,16 +627,12 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
         __syncthreads();                                   // every thread is done with the V slots, weights and sums
         if (BULK && warp == 0)                             // next tile's V blocks land during its K phase
-            stage_bulk(p.v, validV(tile + 1, lane & 3), blkV_of(tile + 1, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
+            stage_bulk(p.v, validV(n_on, n_tile, lane & 3), blkV_of(n_col, n_tile, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
         cur = nxt;
     }
-    if (BULK && tile_lo < tile_hi) {      // the copies issued for the tile after the last one are empty, but their phase must end
-        if (!kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
-        if (!kvc_mbar_wait(&sm.bar[1], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
-    }
 
-    // ---- uncompressed tail (the recent window), handled by the last split: dense fp16 rows
-    if (p.Tr > 0 && split == p.splits - 1) {
+    // ---- uncompressed tail (the recent window), handled with the column's last tiles: dense fp16 rows
+    if (p.Tr > 0 && it.t_hi == n_tiles) {
         float *pt = reinterpret_cast<float *>(sm.w);           // p[row][g] for 256 rows
         for (long long r0 = 0; r0 < p.Tr; r0 += 256) {
             const long long r = r0 + tid;
@@ -676,59 +693,56 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
         }
     }
-    if (flags) atomicOr(p.status, flags);
-
-    // ---- combine the two token groups of the CTA, then the splits
+    // ---- combine the two token groups of the CTA, then the parts of the column
     __syncthreads();
     float *sumbuf = reinterpret_cast<float *>(sm.w);           // [2][128][G]
 #pragma unroll
     for (int g = 0; g < G; g++) sumbuf[(grp * 128 + ch) * G + g] = acc[g];
     __syncthreads();
     const long long head0 = b * Hq + hq0;
-    if (p.splits == 1) {
-        if (tid < 128) {
-#pragma unroll
-            for (int g = 0; g < G; g++) {
-                const float o = (sumbuf[tid * G + g] + sumbuf[(128 + tid) * G + g]) / l_run[g];
-                p.out[(head0 + g) * 128 + tid] = __float2half_rn(o);
-            }
-        }
-        return;
-    }
     if (tid < 128) {
 #pragma unroll
         for (int g = 0; g < G; g++) {
-            float *part = p.ws_part + ((head0 + g) * p.splits + split) * 130;
-            part[2 + tid] = sumbuf[tid * G + g] + sumbuf[(128 + tid) * G + g];
-            if (tid == 0) { part[0] = m_run[g]; part[1] = l_run[g]; }
-        }
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const int done = atomicAdd(&p.ws_count[head0], 1);
-        sm.last = (done == p.splits - 1);
-    }
-    __syncthreads();
-    if (!sm.last) return;
-    __threadfence();
-    if (tid < 128) {
-#pragma unroll
-        for (int g = 0; g < G; g++) {
-            const float *part = p.ws_part + (head0 + g) * p.splits * 130;
-            float M = -CUDART_INF_F;
-            for (int s2 = 0; s2 < p.splits; s2++) M = fmaxf(M, __ldcg(part + s2 * 130));
-            float L = 0.f, O = 0.f;
-            for (int s2 = 0; s2 < p.splits; s2++) {
-                const float m2 = __ldcg(part + s2 * 130);
-                const float e = m2 == -CUDART_INF_F ? 0.f : __expf(m2 - M);
-                L = fmaf(__ldcg(part + s2 * 130 + 1), e, L);
-                O = fmaf(__ldcg(part + s2 * 130 + 2 + tid), e, O);
+            const float o = sumbuf[tid * G + g] + sumbuf[(128 + tid) * G + g];
+            if (p.splits == 1) p.out[(head0 + g) * 128 + tid] = __float2half_rn(o / l_run[g]);
+            else {                                         // a partial result; a second kernel merges the column's
+                float *dst = p.ws_part + ((head0 + g) * p.splits + (int)(j_it % p.splits)) * 130;
+                dst[2 + tid] = o;
+                if (tid == 0) { dst[0] = m_run[g]; dst[1] = l_run[g]; }
             }
-            p.out[(head0 + g) * 128 + tid] = __float2half_rn(O / L);
         }
     }
-    if (tid == 0) p.ws_count[head0] = 0;                       // leave the counters zeroed for the next call
+    if (draw && tid == 0) sm.next_j = drawn;
+    __syncthreads();                                       // the sums are read before the next column's weights overwrite them
+    const long long j_n2 = draw ? 2 * P + sm.next_j : j_n1 + 1;
+    it = nit; have = have_next; j_it = j_n1; j_n1 = j_n2;
+    have_next = have && item_of(j_n1, nit);
+    }   // items of the CTA
+    if (BULK && any_tiles) {              // the copies issued after the last tile are empty, but their phase must end
+        if (!kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
+        if (!kvc_mbar_wait(&sm.bar[1], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
+    }
+    if (flags) atomicOr(p.status, flags);
+    if (draw && tid == 0) {               // the last CTA to finish leaves the scheduling counters zeroed for the next launch
+        __threadfence();
+        if (atomicAdd(&p.sched[1], 1) == (int)gridDim.x - 1) { p.sched[0] = 0; p.sched[1] = 0; __threadfence(); }
+    }
+}
+
+// Merges the `splits` partial results of every head: grid = heads, 128 threads = channels.
+__global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits) {
+    const float *src = ws_part + (size_t)blockIdx.x * splits * 130;
+    const int tid = threadIdx.x;
+    float M = -CUDART_INF_F;
+    for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, src[s2 * 130]);
+    float L = 0.f, O = 0.f;
+    for (int s2 = 0; s2 < splits; s2++) {
+        const float m2 = src[s2 * 130];
+        const float e = m2 == -CUDART_INF_F ? 0.f : __expf(m2 - M);
+        L = fmaf(src[s2 * 130 + 1], e, L);
+        O = fmaf(src[s2 * 130 + 2 + tid], e, O);
+    }
+    out[(size_t)blockIdx.x * 128 + tid] = __float2half_rn(O / L);
 }
 
 template <class K>
@@ -809,21 +823,29 @@ extern "C" int kvc_fused_pv(const kvc_cache *v, int64_t T, int64_t B, int64_t Hk
     return KVC_OK;
 }
 
+// CTAs per SM the attention kernel is launched with at most (its launch bounds ask for this many)
+constexpr int ATTN_CTAS_PER_SM = 3;
+// items a resident CTA should get on average: enough that the draws even out the CTAs' speeds and the
+// last items end close together, few enough that the per-item work (q, partial results) stays small
+constexpr int ATTN_ITEMS_PER_CTA = 4;
+
 extern "C" int kvc_attn_splits(int64_t T, int64_t B, int64_t Hkv, int sm_count) {
     if (T <= 0 || B <= 0 || Hkv <= 0) return 1;
     if (sm_count <= 0) sm_count = kvc_sm_count();
     const long long n_tiles = (T + 255) / 256, cols = B * Hkv;
-    long long want = (8ll * sm_count + cols - 1) / cols;           // several CTAs per resident slot: short tails
-    if (want < 1) want = 1;
-    if (want > n_tiles) want = n_tiles;
-    const long long tps = (n_tiles + want - 1) / want;
+    const long long P = (long long)ATTN_CTAS_PER_SM * sm_count;
+    long long tps = cols * n_tiles / (P * ATTN_ITEMS_PER_CTA);       // tiles per item
+    if (tps < 1) tps = 1;
+    if (tps > n_tiles) tps = n_tiles;
     return (int)((n_tiles + tps - 1) / tps);
 }
 
+// bytes of the zero-initialised head of a workspace: the two scheduling counters
+constexpr int64_t ATTN_COUNTER_BYTES = 256;
+
 extern "C" int64_t kvc_attn_workspace(int64_t B, int64_t Hq, int splits) {
     if (splits < 1) splits = 1;
-    int64_t counters = ((B * Hq * 4 + 255) / 256) * 256;
-    return counters + B * Hq * (int64_t)splits * 130 * 4;
+    return ATTN_COUNTER_BYTES + (splits > 1 ? B * Hq * (int64_t)splits * 130 * 4 : 0);
 }
 
 extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t Hq,
@@ -837,14 +859,15 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     KVC_REQUIRE(T >= 0 && T % 128 == 0, "kvc_attn_decode: the compressed length must be a multiple of 128, got %lld", (long long)T);
     KVC_REQUIRE(Tr >= 0 && (Tr == 0 || (ktail && vtail)), "kvc_attn_decode: tail pointers missing");
     KVC_REQUIRE(T + Tr > 0, "kvc_attn_decode: empty cache");
-    KVC_REQUIRE(B * Hkv <= 65535, "kvc_attn_decode: B*Hkv exceeds the grid limit");
     KVC_REQUIRE(Tr == 0 || ((reinterpret_cast<uintptr_t>(ktail) & 15) == 0), "kvc_attn_decode: ktail must be 16-byte aligned");
-    const long long n_tiles = (T + 255) / 256;
+    const long long n_tiles = (T + 255) / 256, cols = B * Hkv;
+    KVC_REQUIRE(n_tiles < (1ll << 30) && cols < (1ll << 30), "kvc_attn_decode: shape too large");
+    // every column is cut into `splits` runs of `tps` tiles; each (column, run) is one item of work
     if (splits <= 0) splits = kvc_attn_splits(T, B, Hkv, 0);
     if (splits > n_tiles) splits = (int)(n_tiles > 0 ? n_tiles : 1);
-    int tps = (int)((n_tiles + splits - 1) / splits);
-    if (tps < 1) tps = 1;
-    splits = n_tiles > 0 ? (int)((n_tiles + tps - 1) / tps) : 1;
+    const int tps = (int)((n_tiles + splits - 1) / splits);
+    splits = tps > 0 ? (int)((n_tiles + tps - 1) / tps) : 1;
+    KVC_REQUIRE(cols * splits < (1ll << 31) - (1ll << 20), "kvc_attn_decode: too many items");
     if (splits > 1) {
         KVC_REQUIRE(workspace && workspace_bytes >= kvc_attn_workspace(B, Hq, splits),
                     "kvc_attn_decode: workspace needs %lld bytes for %d splits", (long long)kvc_attn_workspace(B, Hq, splits), splits);
@@ -857,8 +880,12 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     p.ktail = reinterpret_cast<const __half *>(ktail); p.vtail = reinterpret_cast<const __half *>(vtail);
     p.out = reinterpret_cast<__half *>(out);
     p.scaling = scaling; p.splits = splits; p.tiles_per_split = tps;
-    p.ws_count = reinterpret_cast<int *>(workspace);
-    p.ws_part = workspace ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) + ((B * Hq * 4 + 255) / 256) * 256) : nullptr;
+    p.n_tiles = (int)n_tiles;
+    p.work = cols * splits;
+    // with a workspace the CTAs draw their items from its counters (zero before the first launch, left zeroed)
+    const bool have_ws = workspace && workspace_bytes >= ATTN_COUNTER_BYTES && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
+    p.sched = have_ws ? reinterpret_cast<int *>(workspace) : nullptr;
+    p.ws_part = have_ws ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) + ATTN_COUNTER_BYTES) : nullptr;
     p.status = status;
     // a slot holds the largest block plus its alignment lead, widened to 16-byte chunks, plus the
     // decoder's two words of read-ahead
@@ -867,21 +894,28 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     const size_t slot_total = 4 * (size_t)(p.slotK_bytes + p.slotV_bytes) + SLOT_PAD;
     // bulk copies widen every block to 16-byte boundaries: both streams must start on one
     const bool bulk = (reinterpret_cast<uintptr_t>(k->encoded) & 15) == 0 && (reinterpret_cast<uintptr_t>(v->encoded) & 15) == 0;
-    const dim3 grid((unsigned)splits, (unsigned)(B * Hkv));
+    const int sms = kvc_sm_count();
     const long long Gt = Hq / Hkv;
     for (long long g0 = 0; g0 < Gt;) {
         const int G = next_chunk(Gt - g0);
         p.g0 = g0;
 #define KVC_AT(GG, BB)                                                                                          \
     {                                                                                                           \
-        if (int rc = set_smem(attn_decode_kernel<GG, BB>, slot_total + sizeof(AttnSmem<GG>))) return rc;        \
-        attn_decode_kernel<GG, BB><<<grid, NTHR, slot_total + sizeof(AttnSmem<GG>), kvc_cu(stream)>>>(p);       \
+        const size_t smem = slot_total + sizeof(AttnSmem<GG>);                                                  \
+        if (int rc = set_smem(attn_decode_kernel<GG, BB>, smem)) return rc;                                     \
+        int occ = 0;                                                                                            \
+        KVC_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, attn_decode_kernel<GG, BB>, NTHR, smem)); \
+        KVC_REQUIRE(occ >= 1, "kvc_attn_decode: %zu bytes of shared memory do not fit an SM", smem);             \
+        long long ctas = (long long)sms * (occ < ATTN_CTAS_PER_SM ? occ : ATTN_CTAS_PER_SM);                    \
+        if (ctas > p.work) ctas = p.work;                                                                       \
+        attn_decode_kernel<GG, BB><<<(unsigned)ctas, NTHR, smem, kvc_cu(stream)>>>(p);                          \
     }
         if (bulk) { if (G == 4) KVC_AT(4, true) else if (G == 2) KVC_AT(2, true) else KVC_AT(1, true) }
         else { if (G == 4) KVC_AT(4, false) else if (G == 2) KVC_AT(2, false) else KVC_AT(1, false) }
 #undef KVC_AT
         g0 += G;
     }
+    if (splits > 1) attn_merge_kernel<<<(unsigned)(B * Hq), 128, 0, kvc_cu(stream)>>>(p.ws_part, p.out, splits);
     KVC_LAUNCH_OK();
     return KVC_OK;
 }
@@ -924,17 +958,17 @@ extern "C" int kvc_attn_decode_static(const kvc_cache *k, const kvc_cache *v, in
                                       const void *q, float scaling, const void *ktail, const void *vtail, int64_t Tr,
                                       void *out, int splits, int32_t *status, kvc_stream_t stream) {
     KVC_REQUIRE(B > 0 && Hkv > 0 && Hq > 0 && T >= 0, "kvc_attn_decode_static: bad shape");
-    if (splits <= 0) splits = kvc_attn_splits(T, B, Hkv, 0);
-    const int64_t need = kvc_attn_workspace(B, Hq, splits);
+    const int parts = splits <= 0 ? kvc_attn_splits(T, B, Hkv, 0) : splits;      // partial results per head
+    const int64_t need = kvc_attn_workspace(B, Hq, parts);
     if (need > KVC_STATIC_SCRATCH_BYTES) {
         kvc_set_error("kvc_attn_decode_static: B=%lld x Hq=%lld x %d splits needs %lld bytes of scratch, the built-in "
                       "array holds %d; lower `splits` or use kvc_attn_decode with a workspace",
-                      (long long)B, (long long)Hq, splits, (long long)need, KVC_STATIC_SCRATCH_BYTES);
+                      (long long)B, (long long)Hq, parts, (long long)need, KVC_STATIC_SCRATCH_BYTES);
         return KVC_ERR_CAPACITY;
     }
     void *scratch = nullptr;
     if (int rc = static_scratch(&scratch)) return rc;
-    // the array keeps whatever the previous call left: the per-head counters must start at zero
-    KVC_CUDA_OK(cudaMemsetAsync(scratch, 0, ((B * Hq * 4 + 255) / 256) * 256, kvc_cu(stream)));
+    // the array keeps whatever the previous call left: the scheduling counters must start at zero
+    KVC_CUDA_OK(cudaMemsetAsync(scratch, 0, ATTN_COUNTER_BYTES, kvc_cu(stream)));
     return kvc_attn_decode(k, v, T, B, Hkv, Hq, q, scaling, ktail, vtail, Tr, out, splits, scratch, need, status, stream);
 }

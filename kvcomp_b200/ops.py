@@ -290,13 +290,17 @@ def attn_decode(kcache, vcache, T, B, Hkv, q, scaling, ktail=None, vtail=None, o
         Tr = ktail.shape[0]
     else:
         ktail = vtail = None
-    if splits <= 0:
-        splits = attn_splits(T, B, Hkv)
+    # splits <= 0: the tiles of all (sequence, KV head) columns are shared evenly among the CTAs that
+    # fit the device (attn_splits = partial results per head to leave room for); splits > 0: every
+    # column is cut into that many equal parts.
     if workspace is None:
-        workspace = attn_workspace(B, Hq, splits, dev)
+        workspace = attn_workspace(B, Hq, splits if splits > 0 else attn_splits(T, B, Hkv), dev)
+    elif workspace is False:        # no workspace at all (splits must be 1): the CTAs take fixed shares of the columns
+        workspace = torch.empty(0, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         _lib.check(lib.kvc_attn_decode(C.byref(kcache), C.byref(vcache), T, B, Hkv, Hq, _p(q), float(scaling),
-                                       _p(ktail), _p(vtail), Tr, _p(out), splits, _p(workspace), workspace.numel(),
+                                       _p(ktail), _p(vtail), Tr, _p(out), int(splits),
+                                       _p(workspace if workspace.numel() else None), workspace.numel(),
                                        _p(status), _stream()), "kvc_attn_decode")
     return out, status
 

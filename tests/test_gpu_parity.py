@@ -337,6 +337,27 @@ def test_attn_decode(ops, kmode, vmode, shared, T, B, Hkv, Hq, Tr, splits, min_d
     assert torch.equal(o1, o2) and torch.equal(o1, out)
 
 
+def test_attn_decode_many_items(ops):
+    """More items than two per resident CTA: the later ones are drawn from the workspace's counter.
+    Every way of sharing the work gives the oracle's result, and the counters end at zero."""
+    T, B, Hkv, Hq = 2048, 8, 16, 16
+    k, v, q = synth(T, B, Hkv, seed=77, Hq=Hq)
+    rk, rv, kc, vc = _caches(ops, k, v, orc.MODE_BLOCK, orc.MODE_TOKEN, 0.05, 0.1, 64, False)
+    scaling = 1.0 / math.sqrt(128)
+    O = orc.attention(*_oracle_q(rk, T, B, Hkv, orc.MODE_BLOCK, 64, False),
+                      *_oracle_q(rv, T, B, Hkv, orc.MODE_TOKEN, 128, False), q, scaling)
+    ws = ops.attn_workspace(B, Hq, 8, "cuda")
+    outs = []
+    for splits, w in ((8, ws), (8, ws), (1, False), (1, ws), (0, None), (3, None)):
+        out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=splits, workspace=w)
+        assert ops.read_status(st) == 0
+        err = np.abs(out.float().cpu().numpy() - O).max() / np.abs(O).max()
+        assert err <= ATTN_RTOL, (splits, err)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[2], outs[3])
+    assert int(ws[:256].view(torch.int32).abs().sum()) == 0
+
+
 def test_attn_decode_unaligned_stream_and_unknown_bound(ops):
     """Streams that do not start on a 16-byte boundary take the plain-load staging path; an unknown
     block bound falls back to the format's maximum.  Same bits either way."""
