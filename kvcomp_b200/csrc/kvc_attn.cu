@@ -11,6 +11,12 @@
 //            (dequantisation folded into the weights, the min_int term summed once per block).
 //   V phase: thread = (128-token group, channel); its vector holds 128 tokens of that channel.
 //            out[ch] = sum_t code_t * ps[t] + zpv, with ps[t] = p[t]*scale[t] staged per group.
+// The attention kernel is launched with as many CTAs as the device holds at once.  Its work is cut into
+// items (one (b, kv head) column x one run of 256-token tiles); a CTA starts with two items fixed by
+// its index and draws the rest from a counter two items ahead, so that the CTAs an SM's schedulers
+// favour take more of them.  Staging copies, tile metadata and the query vector of the next tile or
+// item are always fetched while the current one is decoded.  When a column has more than one item,
+// each leaves a partial result (max, sum, accumulators) and a second kernel merges them.
 // Both phases are "decode 128 symbols and dot them with a shared 128-vector", so they share one
 // decoder.  The shared vector is held in 16-bit block fixed point (one fp32 step per vector, value
 // = step * (256*hi + lo), hi signed and lo unsigned bytes): every table lookup yields up to four
@@ -25,16 +31,13 @@
 
 #include "kvc_decode.cuh"
 
-#ifndef KVC_DEBUG_SKIP
-#define KVC_DEBUG_SKIP 0
-#endif
-
 namespace {
 
 constexpr int SLOT_BYTES = 8192 + 32;     // a block is at most 8191 bytes (u16 fields) + alignment lead
 constexpr int SLOT_PAD = 1024;           // readable bytes behind the last staging slot
 constexpr int WROW = 136;                 // weight words per vector: 128 positions + zeroed overrun (>= 128 + KVC_DECODE_OVERRUN + 1)
 constexpr int NTHR = 256;
+constexpr int ATTN_PART_FLOATS = 4 + 256;   // a partial result of the attention kernel: m, l, two unused, acc[2][128]
 
 struct CacheDev {
     const uint8_t *encoded;
@@ -259,6 +262,17 @@ __device__ __forceinline__ void k_token_unit(unsigned short &sc, int &mi, const 
     sc = kvc_load_scale_bits(m, u); mi = kvc_load_min(m, u);
 }
 
+// sum of each query head's 128 (scaled) values: one warp per head; needs a barrier before and after
+template <int G>
+__device__ __forceinline__ void q_sums(const float *qf, float *qsum, int tid) {
+    if (tid < G * 32) {
+        const int g = tid >> 5, lane = tid & 31;
+        float s = qf[g * 128 + lane] + qf[g * 128 + lane + 32] + qf[g * 128 + lane + 64] + qf[g * 128 + lane + 96];
+        s = kvc_warp_sum(s);
+        if (lane == 0) qsum[g] = s;
+    }
+}
+
 // score of the thread's token from its integer dot products
 template <int G>
 __device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], const int (&lo)[G], const float *step_sub,
@@ -445,7 +459,7 @@ struct AttnParams {
     int splits, tiles_per_split;  // every column is cut into `splits` runs of `tiles_per_split` tiles
     long long work;               // columns * splits items
     uint32_t slotK_bytes, slotV_bytes;   // capacity of one staging slot (multiple of 16)
-    float *ws_part;               // [B*Hq][splits][130]: m, l, acc[128]
+    float *ws_part;               // [B*Hq][splits][ATTN_PART_FLOATS]
     int *sched;                   // {items handed out, CTAs finished}, or null: static shares
     int *status;
 };
@@ -527,12 +541,35 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     TileMeta cur, nxt;
     load_meta(any_tiles, have ? it.col : 0, have ? it.t_lo : 0, cur);
 
+    // The query values of an item are fetched (as fp16 bits) while the item before it still runs.
+    constexpr int QN = (G * 128 + NTHR - 1) / NTHR;
+    unsigned short qn[QN];
+    auto q_fetch = [&](int col_) {
+        const long long row0 = (long long)(col_ / (int)Hkv) * Hq + (long long)(col_ % (int)Hkv) * Gt + p.g0;
+#pragma unroll
+        for (int i = 0; i < QN; i++) {
+            const int idx = tid + i * NTHR;
+            qn[i] = 0;
+            if (idx < G * 128) qn[i] = reinterpret_cast<const unsigned short *>(p.q)[(row0 + (idx >> 7)) * 128 + (idx & 127)];
+        }
+    };
+    auto q_store = [&]() {
+#pragma unroll
+        for (int i = 0; i < QN; i++) {
+            const int idx = tid + i * NTHR;
+            if (idx < G * 128) sm.qf[idx] = kvc_scale_value(qn[i]) * p.scaling;
+        }
+    };
+    if (have) q_fetch(it.col);
+
     uint32_t phase = 0;
     while (have) {
     const int col = it.col, b = col / (int)Hkv, h = col % (int)Hkv;
     const long long hq0 = h * Gt + p.g0;
     if (draw && tid == 0) drawn = atomicAdd(&p.sched[0], 1);
-    load_q<G>(sm.qf, sm.qsum, p.q, b, Hq, hq0, p.scaling, tid);
+    q_store();                                             // fetched during the previous item's last tile
+    __syncthreads();
+    q_sums<G>(sm.qf, sm.qsum, tid);
     __syncthreads();                                       // books, q and (unbuffered) slots are in place
     float m_run[G], l_run[G], acc[G];
 #pragma unroll
@@ -546,12 +583,11 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         const bool actK = t < T, actV = gI * 128 < T;
         // the tile after this one in the CTA's sequence (it may open the next column)
         bool n_on = true; int n_col = col, n_tile = tile + 1;
-        if (n_tile >= it.t_hi) { n_on = have_next && nit.t_lo < nit.t_hi; n_col = n_on ? nit.col : col; n_tile = n_on ? nit.t_lo : 0; }
-#if KVC_DEBUG_SKIP & 16
-        nxt = cur;
-#else
+        if (n_tile >= it.t_hi) {
+            n_on = have_next && nit.t_lo < nit.t_hi; n_col = n_on ? nit.col : col; n_tile = n_on ? nit.t_lo : 0;
+            if (have_next) q_fetch(nit.col);
+        }
         load_meta(n_on, n_col, n_tile, nxt);
-#endif
         if (!BULK) {
             if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
             if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
@@ -566,9 +602,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okK[sub];
-#if !(KVC_DEBUG_SKIP & 1)
             if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, sm.w + sub * 2 * WROW * G, hi, lo);
-#endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
             k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km.sc != 0, kvc_scale_value(cur.ksc), (float)cur.kmi);
         } else {
@@ -613,9 +647,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okV[sub];
-#if !(KVC_DEBUG_SKIP & 2)
             if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, sm.ps + grp * 2 * WROW * G, hi, lo);
-#endif
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
 #pragma unroll
             for (int g = 0; g < G; g++)
@@ -693,23 +725,27 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
         }
     }
-    // ---- combine the two token groups of the CTA, then the parts of the column
-    __syncthreads();
-    float *sumbuf = reinterpret_cast<float *>(sm.w);           // [2][128][G]
-#pragma unroll
-    for (int g = 0; g < G; g++) sumbuf[(grp * 128 + ch) * G + g] = acc[g];
-    __syncthreads();
+    if (it.t_lo >= it.t_hi && have_next) q_fetch(nit.col);     // an item without tiles fetched nothing yet
     const long long head0 = b * Hq + hq0;
-    if (tid < 128) {
+    if (p.splits == 1) {
+        // ---- the item is the whole column: combine the CTA's two token groups and write the output
+        __syncthreads();
+        float *sumbuf = reinterpret_cast<float *>(sm.w);       // [2][128][G]
+#pragma unroll
+        for (int g = 0; g < G; g++) sumbuf[(grp * 128 + ch) * G + g] = acc[g];
+        __syncthreads();
+        if (tid < 128) {
+#pragma unroll
+            for (int g = 0; g < G; g++)
+                p.out[(head0 + g) * 128 + tid] = __float2half_rn((sumbuf[tid * G + g] + sumbuf[(128 + tid) * G + g]) / l_run[g]);
+        }
+    } else {
+        // ---- a partial result {m, l, -, -, acc of group 0 [128], acc of group 1 [128]}; a second kernel merges
 #pragma unroll
         for (int g = 0; g < G; g++) {
-            const float o = sumbuf[tid * G + g] + sumbuf[(128 + tid) * G + g];
-            if (p.splits == 1) p.out[(head0 + g) * 128 + tid] = __float2half_rn(o / l_run[g]);
-            else {                                         // a partial result; a second kernel merges the column's
-                float *dst = p.ws_part + ((head0 + g) * p.splits + (int)(j_it % p.splits)) * 130;
-                dst[2 + tid] = o;
-                if (tid == 0) { dst[0] = m_run[g]; dst[1] = l_run[g]; }
-            }
+            float *dst = p.ws_part + ((head0 + g) * p.splits + (int)(j_it % p.splits)) * ATTN_PART_FLOATS;
+            dst[4 + tid] = acc[g];                             // tid = grp * 128 + ch
+            if (tid == 0) { dst[0] = m_run[g]; dst[1] = l_run[g]; }
         }
     }
     if (draw && tid == 0) sm.next_j = drawn;
@@ -731,16 +767,17 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 
 // Merges the `splits` partial results of every head: grid = heads, 128 threads = channels.
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits) {
-    const float *src = ws_part + (size_t)blockIdx.x * splits * 130;
+    const float *src = ws_part + (size_t)blockIdx.x * splits * ATTN_PART_FLOATS;
     const int tid = threadIdx.x;
     float M = -CUDART_INF_F;
-    for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, src[s2 * 130]);
+    for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, src[s2 * ATTN_PART_FLOATS]);
     float L = 0.f, O = 0.f;
     for (int s2 = 0; s2 < splits; s2++) {
-        const float m2 = src[s2 * 130];
+        const float *pp = src + s2 * ATTN_PART_FLOATS;
+        const float m2 = pp[0];
         const float e = m2 == -CUDART_INF_F ? 0.f : __expf(m2 - M);
-        L = fmaf(src[s2 * 130 + 1], e, L);
-        O = fmaf(src[s2 * 130 + 2 + tid], e, O);
+        L = fmaf(pp[1], e, L);
+        O = fmaf(pp[4 + tid] + pp[4 + 128 + tid], e, O);
     }
     out[(size_t)blockIdx.x * 128 + tid] = __float2half_rn(O / L);
 }
@@ -845,7 +882,7 @@ constexpr int64_t ATTN_COUNTER_BYTES = 256;
 
 extern "C" int64_t kvc_attn_workspace(int64_t B, int64_t Hq, int splits) {
     if (splits < 1) splits = 1;
-    return ATTN_COUNTER_BYTES + (splits > 1 ? B * Hq * (int64_t)splits * 130 * 4 : 0);
+    return ATTN_COUNTER_BYTES + (splits > 1 ? B * Hq * (int64_t)splits * ATTN_PART_FLOATS * 4 : 0);
 }
 
 extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t Hq,
