@@ -78,26 +78,33 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
-// decode the thread's vector (staged at shared address slot_s) and dot it with the weight words at
-// shared address w_s: WROW x G words of hi bytes followed by WROW x G words of lo bytes
+// Where the hi / lo weight word of position c and head g sits in a vector's 2 * WROW * G words.  One or
+// two heads: a record {hi[G], lo[G]} per position, fetched with one 8- or 16-byte load.  Four heads: all
+// hi records, then all lo records (16 bytes each), because 32-byte records would leave half of the banks idle.
+template <int G> __device__ __forceinline__ constexpr int w_hi(int c, int g) { return G == 4 ? c * 4 + g : c * 2 * G + g; }
+template <int G> __device__ __forceinline__ constexpr int w_lo(int c, int g) { return G == 4 ? WROW * 4 + c * 4 + g : c * 2 * G + G + g; }
+
+// decode the thread's vector (staged at shared address slot_s) and dot it with the weight records at
+// shared address w_s (layout: w_hi / w_lo)
 template <int G, bool ESC>
 __device__ __forceinline__ bool decode_dot_impl(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
                                                 uint32_t w_s, int (&hi)[G], int (&lo)[G]) {
-    constexpr uint32_t LO = WROW * G * 4;
-    return kvc_decode_vector<ESC>(slot_s, byte_pos, lut_s, tree_s, [&](uint32_t syms, uint32_t c4) {
+    constexpr int SHIFT = G == 1 ? 3 : 4;                      // log2 of the record's bytes
+    return kvc_decode_vector<ESC, SHIFT>(slot_s, byte_pos, lut_s, tree_s, w_s >> SHIFT, [&](uint32_t syms, uint32_t a) {
         if (G == 4) {
-            const uint4 a = lds128(w_s + c4 * 4), b = lds128(w_s + c4 * 4 + LO);
-            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, b.x, lo[0]);
-            hi[1 % G] = kvc_dp4a_us(syms, a.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, b.y, lo[1 % G]);
-            hi[2 % G] = kvc_dp4a_us(syms, a.z, hi[2 % G]); lo[2 % G] = kvc_dp4a_uu(syms, b.z, lo[2 % G]);
-            hi[3 % G] = kvc_dp4a_us(syms, a.w, hi[3 % G]); lo[3 % G] = kvc_dp4a_uu(syms, b.w, lo[3 % G]);
+            const uint4 x = lds128(a), y = lds128(a + WROW * 16);
+            hi[0] = kvc_dp4a_us(syms, x.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, y.x, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(syms, x.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, y.y, lo[1 % G]);
+            hi[2 % G] = kvc_dp4a_us(syms, x.z, hi[2 % G]); lo[2 % G] = kvc_dp4a_uu(syms, y.z, lo[2 % G]);
+            hi[3 % G] = kvc_dp4a_us(syms, x.w, hi[3 % G]); lo[3 % G] = kvc_dp4a_uu(syms, y.w, lo[3 % G]);
         } else if (G == 2) {
-            const uint2 a = kvc_lds64(w_s + c4 * 2), b = kvc_lds64(w_s + c4 * 2 + LO);
-            hi[0] = kvc_dp4a_us(syms, a.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, b.x, lo[0]);
-            hi[1 % G] = kvc_dp4a_us(syms, a.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, b.y, lo[1 % G]);
+            const uint4 x = lds128(a);
+            hi[0] = kvc_dp4a_us(syms, x.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, x.z, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(syms, x.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(syms, x.w, lo[1 % G]);
         } else {
-            hi[0] = kvc_dp4a_us(syms, kvc_lds32(w_s + c4), hi[0]);
-            lo[0] = kvc_dp4a_uu(syms, kvc_lds32(w_s + c4 + LO), lo[0]);
+            const uint2 x = kvc_lds64(a);
+            hi[0] = kvc_dp4a_us(syms, x.x, hi[0]);
+            lo[0] = kvc_dp4a_uu(syms, x.y, lo[0]);
         }
     });
 }
@@ -165,7 +172,7 @@ __device__ __forceinline__ unsigned short vec_start_bits(const uint16_t *thread_
 }
 
 // ---- K weights --------------------------------------------------------------------------------------
-// Weight words of the 4 blocks of a 256-token tile: w[sub][hi|lo][c][g], step[sub][g], zp[sub][g].
+// Weight records of the 4 blocks of a 256-token tile: w[sub][c][hi|lo][g], step[sub][g], zp[sub][g].
 // Warp `wp` owns block sub = wp & 3 and the query heads g = (wp >> 2) * GH .. + GH - 1 (GH = G/2, or
 // all of them on warps 0-3 when G = 1); lane = 4 consecutive channels.
 // Units that depend on the channel (sc != 0) need tok_div % 64 == 0 so that a block shares them;
@@ -220,13 +227,13 @@ __device__ __forceinline__ void k_weights_build(uint32_t *w, float *step, float 
             int nv = __shfl_down_sync(0xffffffffu, q4[i], 1);
             q4[4 + i] = lane == 31 ? 0 : nv;
         }
-        uint32_t *row = w + (size_t)sub * 2 * WROW * G;           // hi words, then lo words
+        uint32_t *row = w + (size_t)sub * 2 * WROW * G;           // layout: w_hi / w_lo
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const uint2 r = pack4(q4[i], q4[i + 1], q4[i + 2], q4[i + 3]);
-            row[(lane * 4 + i) * G + g] = r.x; row[WROW * G + (lane * 4 + i) * G + g] = r.y;
+            row[w_hi<G>(lane * 4 + i, g)] = r.x; row[w_lo<G>(lane * 4 + i, g)] = r.y;
         }
-        if (lane < WROW - 128) { row[(128 + lane) * G + g] = 0u; row[WROW * G + (128 + lane) * G + g] = 0u; }
+        if (lane < WROW - 128) { row[w_hi<G>(128 + lane, g)] = 0u; row[w_lo<G>(128 + lane, g)] = 0u; }
         if (lane == 0) { step[sub * G + g] = st; zp[sub * G + g] = z; }
     }
 }
@@ -286,7 +293,7 @@ __device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], cons
 
 // ---- V weights --------------------------------------------------------------------------------------
 // Called by all 256 threads (thread = token of the tile, grp = its 128-token group, tl = its index in
-// the group) with wv[g] = p[g] * scale of the token.  Builds records ps[grp][tl][g], step[grp][g].
+// the group) with wv[g] = p[g] * scale of the token.  Builds records ps[grp][tl][hi|lo][g], step[grp][g].
 // `red` is scratch for 8*G floats, `q16` for 2*G*(128+4) int16.  Contains three block barriers.
 template <int G>
 __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red, int16_t *q16, const float (&wv)[G],
@@ -308,10 +315,10 @@ __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const int16_t *qq = q16 + (grp * G + g) * 132 + tl;
-        uint32_t *row = ps + (size_t)grp * 2 * WROW * G;          // hi words, then lo words
+        uint32_t *row = ps + (size_t)grp * 2 * WROW * G;          // layout: w_hi / w_lo
         const uint2 r = pack4(qq[0], qq[1], qq[2], qq[3]);
-        row[tl * G + g] = r.x; row[WROW * G + tl * G + g] = r.y;
-        if (tl < WROW - 128) { row[(128 + tl) * G + g] = 0u; row[WROW * G + (128 + tl) * G + g] = 0u; }
+        row[w_hi<G>(tl, g)] = r.x; row[w_lo<G>(tl, g)] = r.y;
+        if (tl < WROW - 128) { row[w_hi<G>(128 + tl, g)] = 0u; row[w_lo<G>(128 + tl, g)] = 0u; }
     }
     __syncthreads();
 }
@@ -321,7 +328,7 @@ template <int G>
 struct QkSmem {
     KvcBookSmem book;
     uint8_t slot[4][SLOT_BYTES];
-    uint32_t w[4 * 2 * WROW * G];
+    alignas(32) uint32_t w[4 * 2 * WROW * G];
     float step[4 * G];
     float zp[4 * G];
     float qf[G * 128];
@@ -334,7 +341,7 @@ template <int G>
 __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T, long long B, long long Hkv, long long Hq,
                                                         long long g0, const __half *__restrict__ q, void *__restrict__ out,
                                                         int out_f32, int *__restrict__ status) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     QkSmem<G> &sm = *reinterpret_cast<QkSmem<G> *>(smem_raw);
     const int tid = threadIdx.x, sub = tid >> 6, v = tid & 63;
     const long long cols = B * Hkv, col = blockIdx.y, b = col / Hkv, h = col % Hkv;
@@ -373,7 +380,7 @@ template <int G>
 struct PvSmem {
     KvcBookSmem book;
     uint8_t slot[4][SLOT_BYTES];
-    uint32_t ps[2 * 2 * WROW * G];
+    alignas(32) uint32_t ps[2 * 2 * WROW * G];
     float vstep[2 * G];
     float zpv[2 * G];
     float red[2][8 * G];
@@ -386,7 +393,7 @@ template <int G>
 __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T, long long B, long long Hkv, long long Hq,
                                                         long long g0, const __half *__restrict__ P, __half *__restrict__ out,
                                                         int *__restrict__ status) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     PvSmem<G> &sm = *reinterpret_cast<PvSmem<G> *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
     const int grp = tid >> 7, ch = tid & 127;
@@ -433,10 +440,10 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
 
 // ---- one-pass decode attention -------------------------------------------------------------------
 template <int G>
-struct alignas(16) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch) and
+struct alignas(32) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch) and
     KvcBookSmem bookK, bookV;         // SLOT_PAD bytes that a corrupt stream's decoder overrun may read
-    uint32_t w[4 * 2 * WROW * G];     // K weight words; reused for the tail and the final cross-group sum
-    uint32_t ps[2 * 2 * WROW * G];    // V weight words
+    alignas(32) uint32_t w[4 * 2 * WROW * G];     // K weight records; reused for the tail and the final cross-group sum
+    alignas(32) uint32_t ps[2 * 2 * WROW * G];    // V weight records
     float kstep[4 * G], zp[4 * G];
     float vstep[2 * G];
     float qf[G * 128];
@@ -467,7 +474,7 @@ struct AttnParams {
 // BULK: stage with bulk asynchronous copies (one tile phase ahead) instead of plain loads.
 template <int G, bool BULK>
 __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     AttnSmem<G> &sm = *reinterpret_cast<AttnSmem<G> *>(smem_raw);
     uint8_t *const slotsK = smem_raw + sizeof(AttnSmem<G>), *const slotsV = slotsK + 4 * p.slotK_bytes;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;

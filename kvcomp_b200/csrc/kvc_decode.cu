@@ -43,12 +43,12 @@ __global__ void __launch_bounds__(256) decode_kernel(
             uint8_t *trow = sm.tile[sub] + v * TILE_STRIDE;
             bool ok = start < nbytes;
             if (ok)
-                ok = kvc_decode_vector<true>(kvc_smem_addr(sm.slot[sub]), lead + start, kvc_smem_addr(sm.book.lut),
-                                             kvc_smem_addr(sm.book.tree),
-                                             [&](uint32_t e, uint32_t c4) {
+                ok = kvc_decode_vector<true, 0>(kvc_smem_addr(sm.slot[sub]), lead + start, kvc_smem_addr(sm.book.lut),
+                                             kvc_smem_addr(sm.book.tree), 0u,
+                                             [&](uint32_t e, uint32_t c) {
                                                  // three byte stores; bytes past the lookup's symbols are rewritten
                                                  // by the next lookup, bytes past position 127 land in the row padding
-                                                 uint8_t *d = trow + (c4 >> 2);
+                                                 uint8_t *d = trow + c;
                                                  d[0] = (uint8_t)(e >> 8); d[1] = (uint8_t)(e >> 16); d[2] = (uint8_t)(e >> 24);
                                              });
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;

@@ -103,20 +103,24 @@ __device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
 // where the vector starts in it; lut_s / tree_s: shared-space addresses of the book's tables.
 // The decoder state is (position << 6) | bit offset into the (hi, lo) register pair, so applying a
 // table entry is one add of its low byte.
-// emit(e, c4): `e` holds up to three symbols in bytes 1..3 for positions c..c+2 of the vector (unused
-// bytes are 0; byte 0 is the table entry's advance byte and must be ignored), c4 = c * 4 (the byte
-// offset of a 4-byte weight word).  The end
-// of the vector is tested once per KVC_DECODE_UNROLL lookups, so emit may be handed symbols for
+// emit(e, a): `e` holds up to three symbols in bytes 1..3 for positions c..c+2 of the vector (unused
+// bytes are 0; byte 0 is the table entry's advance byte and must be ignored); a = (base + c) << SHIFT:
+// the position counter starts at `base`, so a consumer that keeps one record of 2^SHIFT bytes per
+// position at shared address A passes base = A >> SHIFT and gets the record's address with no add.
+// The end of the vector is tested once per KVC_DECODE_UNROLL lookups, so emit may be handed symbols for
 // positions up to 127 + KVC_DECODE_OVERRUN; the consumer keeps room for them (zero weights, padding).
 // ESC = false is for books whose longest code fits the table window: no escape test in the loop.
 // Every round advances by at least one symbol, so the loop ends after at most 128 rounds; a corrupt
 // stream can read at most a few hundred bytes past its vector, for which the kernels keep padding
 // behind the last slot.  Returns false when the bits do not form valid codes.
-template <bool ESC, class Emit>
+template <bool ESC, int SHIFT, class Emit>
 __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
-                                                  Emit emit) {
+                                                  uint32_t base, Emit emit) {
+    static_assert(SHIFT >= 0 && SHIFT <= 6, "record size");
+    constexpr uint32_t AMASK = 0xffffffffu << SHIFT;       // drops the bit-offset bits left below the position
+    const uint32_t end = (base + KVC_VEC_LEN) << 6;
     uint32_t ptr = slot_s + (byte_pos & ~3u);
-    uint32_t state = (byte_pos & 3u) << 3;
+    uint32_t state = (base << 6) | ((byte_pos & 3u) << 3);
     uint32_t hi = kvc_bswap(kvc_lds32(ptr)), lo = kvc_bswap(kvc_lds32(ptr + 4));
     uint32_t nxt = kvc_lds32(ptr + 8);     // one word of read-ahead keeps the refill off the critical path
     ptr += 12;
@@ -127,12 +131,12 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
         const uint32_t win = __funnelshift_l(lo, hi, state);          // the shift uses the low 5 bits
         const uint32_t e = kvc_lds32(lut_s + ((win >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
         if (!ESC || (e & 0xffu) != 0) {
-            emit(e, (state >> 4) & 0x3fcu);                           // bit offset < 64: (c << 6) >> 4 = c * 4
+            emit(e, (state >> (6 - SHIFT)) & AMASK);
             state = (uint32_t)kvc_dp4a_uu(e, 1u, (int)state);         // state += byte 0 of e, off the integer ALU pipe
         } else {                                                      // code longer than the window
             uint32_t node = e >> 8, sym = 0;
             bool found = false;
-            const uint32_t c4 = (state >> 4) & 0x3fcu;
+            const uint32_t a = (state >> (6 - SHIFT)) & AMASK;
             state += KVC_LUT_BITS;
             for (int guard = 0; guard < 40; guard++) {
                 if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
@@ -144,11 +148,11 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
                 node = (nd >> (16 * bit)) & 0xffffu;
             }
             ok = ok && found;
-            emit(sym << 8, c4);
+            emit(sym << 8, a);
             state += 1u << 6;
         }
         if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
       }
-    } while (state < (KVC_VEC_LEN << 6));
+    } while (state < end);
     return ok;
 }
