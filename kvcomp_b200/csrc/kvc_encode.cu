@@ -1,12 +1,13 @@
 // Blocked Huffman encoder (kernels.cu:181-235, 419-596 restated for sm_100a).
 //
 // Three phases, no inter-CTA waiting and a deterministic stream:
-//   A  sizes   one CTA per block: stage the 64x128 code tile in shared memory, a warp per
-//              vector sums code lengths with shuffles -> thread_info, block byte count
+//   A  sizes   one 64-thread CTA per block: stage the 64x128 code tile in shared memory, a thread
+//              per vector sums its code lengths, a two-warp scan -> thread_info, block byte count
 //   B  scan    exclusive prefix sum of block byte counts -> block_info offsets (ascending id)
-//   C  emit    one CTA per block: each lane places its 4 codes at their bit offsets (warp-shuffle
-//              prefix sum of lengths) into a shared-memory image of the block that is aligned
-//              like its destination, then the image goes out as 128-bit stores
+//   C  emit    one 64-thread CTA per block: a thread per vector shifts its codes through a 64-bit
+//              register and writes whole words into a shared-memory image of the block that is
+//              aligned like its destination (only the first and last word of a vector, which it
+//              may share with its neighbours, are OR-ed in); the image goes out as 128-bit stores
 #include "kvc_common.cuh"
 
 namespace {
@@ -14,15 +15,7 @@ namespace {
 constexpr int TILE_STRIDE = 132;                  // bytes per vector row in shared memory (padded)
 constexpr int OUT_CAP = 8192 + 32;                // block image: 8191 bytes max + alignment lead + slack
 
-struct EncTable { uint32_t code[256]; uint32_t len[256]; };
-
-__device__ __forceinline__ void load_table(EncTable &t, const uint32_t *__restrict__ enc, int n_entries, int tid, int nthr) {
-    for (int i = tid; i < 256; i += nthr) {
-        bool ok = i < n_entries;
-        t.code[i] = ok ? enc[2 * i] : 0u;
-        t.len[i] = ok ? enc[2 * i + 1] : 0u;
-    }
-}
+constexpr int ENC_THREADS = 64;                   // one thread per vector of the block
 
 // Stage the code tile of block `blk` as tile[vector][symbol].
 // K: vector v = token 64j+v, symbols = its 128 channels (rows of 128 contiguous bytes).
@@ -33,7 +26,8 @@ __device__ __forceinline__ void stage_tile(uint8_t *tile, const uint8_t *__restr
     if (is_k) {
         const long long j = blk / cols, col = blk % cols;
         const uint8_t *src = codes + (j * 64) * row + col * 128;
-        for (int i = tid; i < 64 * 32; i += 256) {             // 64 rows x 32 words
+#pragma unroll 8
+        for (int i = tid; i < 64 * 32; i += ENC_THREADS) {     // 64 rows x 32 words
             int v = i >> 5, w = i & 31;
             uint32_t x = *reinterpret_cast<const uint32_t *>(src + v * row + w * 4);
             *reinterpret_cast<uint32_t *>(tile + v * TILE_STRIDE + w * 4) = x;
@@ -41,7 +35,8 @@ __device__ __forceinline__ void stage_tile(uint8_t *tile, const uint8_t *__restr
     } else {
         const long long g = blk / (cols * 2), m = blk % (cols * 2);
         const uint8_t *src = codes + (g * 128) * row + m * 64;
-        for (int i = tid; i < 128 * 16; i += 256) {            // 128 token rows x 16 words
+#pragma unroll 8
+        for (int i = tid; i < 128 * 16; i += ENC_THREADS) {    // 128 token rows x 16 words
             int t = i >> 4, w = i & 15;
             uint32_t x = *reinterpret_cast<const uint32_t *>(src + t * row + w * 4);
 #pragma unroll
@@ -59,47 +54,47 @@ __device__ __forceinline__ uint32_t warp_excl_scan(uint32_t v, int lane, uint32_
 }
 
 // ---- phase A ----------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) encode_sizes_kernel(
+__global__ void __launch_bounds__(ENC_THREADS) encode_sizes_kernel(
     const uint8_t *__restrict__ codes, long long cols, int is_k, const uint32_t *__restrict__ enc, int n_entries,
     uint16_t *__restrict__ thread_info, uint32_t *__restrict__ sizes, unsigned long long *__restrict__ partial,
     unsigned long long *__restrict__ max_block, int *__restrict__ status) {
     __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE];
-    __shared__ EncTable tab;
-    __shared__ uint32_t vbits[64];
+    __shared__ uint8_t lens[256];
+    __shared__ uint32_t wsum[2];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long blk = blockIdx.x;
-    load_table(tab, enc, n_entries, tid, 256);
+    for (int i = tid; i < 256; i += ENC_THREADS) lens[i] = i < n_entries ? (uint8_t)min(enc[2 * i + 1], 255u) : (uint8_t)0;
     stage_tile(tile, codes, blk, cols, is_k, tid);
     __syncthreads();
     int flags = 0;
-    for (int v = warp; v < 64; v += 8) {
-        uint32_t x = *reinterpret_cast<const uint32_t *>(tile + v * TILE_STRIDE + lane * 4);
-        uint32_t bits = 0;
+    uint32_t bits = 0;
+    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(tile + tid * TILE_STRIDE);
+#pragma unroll 8
+    for (int w = 0; w < 32; w++) {
+        const uint32_t x = rowp[w];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            uint32_t l = tab.len[(x >> (8 * k)) & 0xffu];
+            const uint32_t l = lens[(x >> (8 * k)) & 0xffu];
             if (l == 0) flags |= KVC_FLAG_SYMBOL_MISSING;
             bits += l;
         }
-        bits = (uint32_t)__reduce_add_sync(0xffffffffu, bits);
-        if (lane == 0) vbits[v] = bits;
     }
+    const uint32_t n = (bits + 7) >> 3;                      // the vector's bytes
+    if (n > (is_k ? 128u : 256u)) flags |= KVC_FLAG_VECTOR_LONG;
+    uint32_t wtotal;
+    uint32_t start = warp_excl_scan(n, lane, &wtotal);
+    if (lane == 31) wsum[warp] = wtotal;
     __syncthreads();
-    if (warp == 0) {       // byte offsets of the 64 vectors: two per lane
-        uint32_t b0 = vbits[2 * lane], b1 = vbits[2 * lane + 1];
-        uint32_t n0 = (b0 + 7) >> 3, n1 = (b1 + 7) >> 3, total;
-        uint32_t start = warp_excl_scan(n0 + n1, lane, &total);
-        uint32_t e0 = start + n0, e1 = e0 + n1;
-        if (n0 > (is_k ? 128u : 256u) || n1 > (is_k ? 128u : 256u)) flags |= KVC_FLAG_VECTOR_LONG;
-        // kernels.cu:462-465: (end byte << 3) + pad bits
-        thread_info[blk * 64 + 2 * lane] = (uint16_t)((e0 << 3) + (n0 * 8 - b0));
-        thread_info[blk * 64 + 2 * lane + 1] = (uint16_t)((e1 << 3) + (n1 * 8 - b1));
-        if (lane == 0) {
-            sizes[blk] = total;
-            atomicAdd(&partial[blk >> 10], (unsigned long long)total);
-            if (max_block) atomicMax(max_block, (unsigned long long)total);
-            if (total > 8191u) flags |= KVC_FLAG_BLOCK_LONG;
-        }
+    if (warp == 1) start += wsum[0];
+    const uint32_t end = start + n;
+    // kernels.cu:462-465: (end byte << 3) + pad bits
+    thread_info[blk * 64 + tid] = (uint16_t)((end << 3) + (n * 8 - bits));
+    if (tid == 63) {
+        const uint32_t total = end;
+        sizes[blk] = total;
+        atomicAdd(&partial[blk >> 10], (unsigned long long)total);
+        if (max_block) atomicMax(max_block, (unsigned long long)total);
+        if (total > 8191u) flags |= KVC_FLAG_BLOCK_LONG;
     }
     if (flags) atomicOr(status, flags);
 }
@@ -160,56 +155,80 @@ __global__ void __launch_bounds__(1024) scan_blocks_kernel(const uint32_t *__res
     }
 }
 
+// Thread = vector: encode the 128 symbols at rowp into the block image `out`, starting at byte `start`.
+// SHORT: no code is longer than 16 bits.
+template <bool SHORT>
+__device__ __forceinline__ void encode_vector(const uint32_t *rowp, const uint2 *tab, uint32_t *out, uint32_t start) {
+    // acc collects code bits below the `have` bits it already holds; whole words leave from the top
+    uint32_t wp = start >> 2, have = (start & 3u) * 8;   // the first word's leading bytes belong to the vector before
+    unsigned long long acc = 0;
+    bool shared_word = true;                            // the next word to leave may be shared with a neighbour
+    auto flush = [&]() {
+        have -= 32u;
+        const uint32_t word = (uint32_t)(acc >> have);
+        if (shared_word) { atomicOr(&out[wp], word); shared_word = false; }
+        else out[wp] = word;
+        wp++;
+    };
+#pragma unroll 2
+    for (int w = 0; w < 32; w++) {
+        const uint32_t x = rowp[w];
+        const uint2 e0 = tab[x & 0xffu], e1 = tab[(x >> 8) & 0xffu], e2 = tab[(x >> 16) & 0xffu], e3 = tab[x >> 24];
+        if (SHORT) {
+            // codes of at most 16 bits: two of them make one piece of at most 32 bits, one test per pair
+            // (a missing symbol has length 0 and code 0: nothing changes)
+            const uint32_t la = e0.y + e1.y, lb = e2.y + e3.y;
+            const uint32_t pa = (e0.x << e1.y) | e1.x, pb = (e2.x << e3.y) | e3.x;
+            acc = (acc << la) | pa; have += la;
+            if (have >= 32u) flush();
+            acc = (acc << lb) | pb; have += lb;
+            if (have >= 32u) flush();
+        } else {
+            acc = (acc << e0.y) | e0.x; have += e0.y; if (have >= 32u) flush();
+            acc = (acc << e1.y) | e1.x; have += e1.y; if (have >= 32u) flush();
+            acc = (acc << e2.y) | e2.x; have += e2.y; if (have >= 32u) flush();
+            acc = (acc << e3.y) | e3.x; have += e3.y; if (have >= 32u) flush();
+        }
+    }
+    if (have) atomicOr(&out[wp], (uint32_t)(acc << (32u - have)));   // the tail, zero-padded to a byte by the next start
+}
+
 // ---- phase C ----------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) encode_emit_kernel(
+__global__ void __launch_bounds__(ENC_THREADS) encode_emit_kernel(
     const uint8_t *__restrict__ codes, long long cols, int is_k, const uint32_t *__restrict__ enc, int n_entries,
     const uint16_t *__restrict__ thread_info, const uint2 *__restrict__ block_info,
     const uint32_t *__restrict__ sizes, uint32_t base_offset, uint8_t *__restrict__ encoded, long long capacity) {
     __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE];
     __shared__ __align__(16) uint32_t out[OUT_CAP / 4];
-    __shared__ EncTable tab;
+    __shared__ uint2 tab[256];                              // {code, length}
     __shared__ uint16_t tinfo[64];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const long long blk = blockIdx.x;
     const uint2 bi = block_info[blk];
     const long long off = (long long)bi.x - base_offset;
     const uint32_t nbytes = sizes[blk];
     // an oversized block cannot be described by its u16 fields; a full stream has no room: skip
     if (nbytes > 8191u || off + nbytes > capacity) return;
-    load_table(tab, enc, n_entries, tid, 256);
+    int too_long = 0;
+    for (int i = tid; i < 256; i += ENC_THREADS) {
+        tab[i] = i < n_entries ? make_uint2(enc[2 * i], enc[2 * i + 1]) : make_uint2(0u, 0u);
+        too_long |= tab[i].y > 16u;
+    }
     stage_tile(tile, codes, blk, cols, is_k, tid);
-    if (tid < 64) tinfo[tid] = thread_info[blk * 64 + tid];
-    for (int i = tid; i < OUT_CAP / 4; i += 256) out[i] = 0;
-    __syncthreads();
+    tinfo[tid] = thread_info[blk * 64 + tid];
     uint8_t *dst = encoded + off;
     const uint32_t lead = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15);   // image is aligned like dst
-    for (int v = warp; v < 64; v += 8) {
-        uint32_t x = *reinterpret_cast<const uint32_t *>(tile + v * TILE_STRIDE + lane * 4);
-        uint32_t c[4], l[4], bits = 0;
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            uint32_t s = (x >> (8 * k)) & 0xffu;
-            c[k] = tab.code[s]; l[k] = tab.len[s]; bits += l[k];
-        }
-        uint32_t total;
-        uint32_t p = warp_excl_scan(bits, lane, &total);
-        p += 8u * (lead + (v ? (uint32_t)(tinfo[v - 1] >> 3) : 0u));
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            if (l[k]) {
-                uint32_t w = p >> 5, s = p & 31u;
-                unsigned long long val = (unsigned long long)c[k] << (64 - l[k] - s);
-                atomicOr(&out[w], (uint32_t)(val >> 32));
-                if ((uint32_t)val) atomicOr(&out[w + 1], (uint32_t)val);
-                p += l[k];
-            }
-        }
-    }
+    const uint32_t end = lead + nbytes;
+    for (uint32_t i = tid; i * 16 < end + 4; i += ENC_THREADS) reinterpret_cast<uint4 *>(out)[i] = make_uint4(0u, 0u, 0u, 0u);
+    const bool long_codes = __syncthreads_or(too_long) != 0;
+    const uint32_t start = lead + (tid ? (uint32_t)(tinfo[tid - 1] >> 3) : 0u);
+    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(tile + tid * TILE_STRIDE);
+    if (long_codes) encode_vector<false>(rowp, tab, out, start);
+    else encode_vector<true>(rowp, tab, out, start);
     __syncthreads();
     // image words hold stream bytes most-significant first; swap to memory order on the way out
-    const uint32_t end = lead + nbytes;
     uint8_t *g0 = dst - lead;                                   // 16-byte aligned
-    for (uint32_t ch = tid; ch * 16 < end; ch += 256) {
+    for (uint32_t ch = tid; ch * 16 < end; ch += ENC_THREADS) {
         uint32_t b0 = ch * 16, b1 = b0 + 16;
         uint4 wv = *reinterpret_cast<const uint4 *>(&out[ch * 4]);
         wv.x = kvc_bswap(wv.x); wv.y = kvc_bswap(wv.y); wv.z = kvc_bswap(wv.z); wv.w = kvc_bswap(wv.w);
@@ -258,12 +277,12 @@ extern "C" int kvc_encode(const uint8_t *codes, int64_t T, int64_t cols, int is_
         reinterpret_cast<uint8_t *>(workspace) + ((nblk * 4 + 15) / 16) * 16);
     const uint32_t *enc = reinterpret_cast<const uint32_t *>(enc_table);
     KVC_CUDA_OK(cudaMemsetAsync(partial, 0, (n_part + 1) * 8, s));
-    encode_sizes_kernel<<<(unsigned)nblk, 256, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info, sizes, partial,
+    encode_sizes_kernel<<<(unsigned)nblk, ENC_THREADS, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info, sizes, partial,
                                                       total_bytes ? total_bytes + 1 : nullptr, status);
     scan_partials_kernel<<<1, 1024, 0, s>>>(partial, n_part, total_bytes);
     scan_blocks_kernel<<<(unsigned)n_part, 1024, 0, s>>>(sizes, nblk, partial, base_offset, encoded_capacity,
                                                         reinterpret_cast<uint2 *>(block_info), status);
-    encode_emit_kernel<<<(unsigned)nblk, 256, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info,
+    encode_emit_kernel<<<(unsigned)nblk, ENC_THREADS, 0, s>>>(codes, cols, is_k, enc, n_entries, thread_info,
                                                      reinterpret_cast<const uint2 *>(block_info), sizes, base_offset,
                                                      encoded, encoded_capacity);
     KVC_LAUNCH_OK();

@@ -4,6 +4,8 @@
 // elementwise op widens to fp32, computes, and rounds to nearest-even back to fp16; the
 // Python scalar `rel` stays fp32.  Explicit round-to-nearest intrinsics are used so that no
 // contraction or fast-math rewrite can change a bit.
+#include <algorithm>
+
 #include "kvc_common.cuh"
 
 namespace {
@@ -64,10 +66,18 @@ __device__ __forceinline__ uint2 quant_eight(const uint4 &v, const UnitParam *p,
     return o;
 }
 
-__device__ __forceinline__ void hist_flush(unsigned int *sh, unsigned long long *gh, int tid, int nthr) {
+// The CTA's bins are private to each warp (sh[warp][256]): fewer lanes meet on a counter.
+__device__ __forceinline__ void hist_clear(unsigned int *sh, int tid, int nthr) {
+    for (int i = tid; i < (nthr / 32) * 256; i += nthr) sh[i] = 0;
     __syncthreads();
-    for (int i = tid; i < 256; i += nthr)
-        if (sh[i]) atomicAdd(&gh[i], (unsigned long long)sh[i]);
+}
+__device__ __forceinline__ void hist_flush(const unsigned int *sh, unsigned long long *gh, int tid, int nthr) {
+    __syncthreads();
+    for (int i = tid; i < 256; i += nthr) {
+        unsigned int c = 0;
+        for (int w = 0; w < nthr / 32; w++) c += sh[w * 256 + i];
+        if (c) atomicAdd(&gh[i], (unsigned long long)c);
+    }
 }
 
 __device__ __forceinline__ void minmax8(const uint4 &v, float &mn, float &mx) {
@@ -78,6 +88,7 @@ __device__ __forceinline__ void minmax8(const uint4 &v, float &mn, float &mx) {
 
 // ---- ChannelQuant (utils/compute.py:140): one unit per (token block, b, h, channel) -------------
 // CTA = one (j, b, h) tile of blk tokens x 128 channels; thread = 8 channels x every 8th token.
+// (Walking several tiles per CTA to clear and flush the histogram bins less often measured slower.)
 __global__ void __launch_bounds__(128) quant_channel_kernel(
     const __half *__restrict__ x, long long B, long long H, int blk, float rel,
     uint8_t *__restrict__ codes, void *__restrict__ min_int, int min_bytes, __half *__restrict__ scale,
@@ -85,11 +96,12 @@ __global__ void __launch_bounds__(128) quant_channel_kernel(
     __shared__ float smn[8][128], smx[8][128];
     __shared__ unsigned int shist[256];
     const int tid = threadIdx.x, cg = tid & 15, r = tid >> 4;
+    const long long row_stride = B * H * 128;
+    if (ghist) { for (int i = tid; i < 256; i += 128) shist[i] = 0; }      // a barrier follows before the first count
+    int flags = 0;
     const long long tile = blockIdx.x;                 // (j * B + b) * H + h
     const long long h = tile % H, b = (tile / H) % B, j = tile / (H * B);
-    const long long row_stride = B * H * 128;
     const long long base = ((j * blk) * B + b) * H * 128 + h * 128 + cg * 8;
-    if (ghist) { for (int i = tid; i < 256; i += 128) shist[i] = 0; }
     float mn[8], mx[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) { mn[i] = INFINITY; mx[i] = -INFINITY; }
@@ -102,28 +114,33 @@ __global__ void __launch_bounds__(128) quant_channel_kernel(
 #pragma unroll
     for (int k = 0; k < 8; k++) { smn[r][cg * 8 + k] = mn[k]; smx[r][cg * 8 + k] = mx[k]; }
     __syncthreads();
-    int flags = 0;
+    {   // thread = channel: fold the 8 partials, derive the unit's parameters once, share them
+        float a = smn[0][tid], z = smx[0][tid];
+#pragma unroll
+        for (int rr = 1; rr < 8; rr++) { a = fminf(a, smn[rr][tid]); z = fmaxf(z, smx[rr][tid]); }
+        __half sc;
+        const UnitParam q = unit_param(a, z, rel, &sc, &flags);
+        const long long u = tile * 128 + tid;
+        scale[u] = sc;
+        store_min(min_int, min_bytes, u, q.mi, &flags);
+        __syncthreads();                                   // every partial is read before the rows are reused
+        smn[0][tid] = q.sf; smn[1][tid] = q.mi; smn[2][tid] = q.rcp;
+    }
+    __syncthreads();
     UnitParam p[8];
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
-        float a = smn[0][cg * 8 + k], z = smx[0][cg * 8 + k];
-#pragma unroll
-        for (int rr = 1; rr < 8; rr++) { a = fminf(a, smn[rr][cg * 8 + k]); z = fmaxf(z, smx[rr][cg * 8 + k]); }
-        __half sc;
-        p[k] = unit_param(a, z, rel, &sc, &flags);
-        if (r == 0) {
-            long long u = tile * 128 + cg * 8 + k;
-            scale[u] = sc;
-            store_min(min_int, min_bytes, u, p[k].mi, &flags);
-        }
-    }
+    for (int k = 0; k < 8; k++) { p[k].sf = smn[0][cg * 8 + k]; p[k].mi = smn[1][cg * 8 + k]; p[k].rcp = smn[2][cg * 8 + k]; }
     for (int i = r; i < blk; i += 8) {
         uint4 v = *reinterpret_cast<const uint4 *>(x + base + i * row_stride);
         uint2 o = quant_eight(v, p, 1, &flags, ghist ? shist : nullptr);
         *reinterpret_cast<uint2 *>(codes + base + i * row_stride) = o;
     }
     if (flags) atomicOr(status, flags);
-    if (ghist) hist_flush(shist, ghist, tid, 128);
+    if (ghist) {
+        __syncthreads();
+        for (int i = tid; i < 256; i += 128)
+            if (shist[i]) atomicAdd(&ghist[i], (unsigned long long)shist[i]);
+    }
 }
 
 // ---- units that are contiguous runs of `ulen` elements -----------------------------------------
@@ -135,12 +152,12 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(
     uint8_t *__restrict__ codes, void *__restrict__ min_int, int min_bytes, __half *__restrict__ scale,
     unsigned long long *__restrict__ ghist, int *__restrict__ status) {
     __shared__ float red[2][8];
-    __shared__ unsigned int shist[256];
+    __shared__ unsigned int shist[8 * 256];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int UNITS_PER_CTA = 256 / GROUP;
     const long long u = (long long)blockIdx.x * UNITS_PER_CTA + (GROUP == 256 ? 0 : warp);
     const int gl = GROUP == 256 ? tid : lane;          // index inside the group
-    if (ghist) { for (int i = tid; i < 256; i += 256) shist[i] = 0; __syncthreads(); }
+    if (ghist) hist_clear(shist, tid, 256);
     const bool active = u < n_units;
     const long long chunks = ulen / 8;
     const __half *xu = x + u * ulen;
@@ -165,12 +182,67 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(
         if (gl == 0) { scale[u] = sc; store_min(min_int, min_bytes, u, p.mi, &flags); }
         for (long long k = gl; k < chunks; k += GROUP) {
             uint4 v = *reinterpret_cast<const uint4 *>(xu + k * 8);
-            uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist : nullptr);
+            uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist + warp * 256 : nullptr);
             *reinterpret_cast<uint2 *>(codes + u * ulen + k * 8) = o;
         }
     }
     if (flags) atomicOr(status, flags);
     if (ghist) hist_flush(shist, ghist, tid, 256);
+}
+
+// Units of CH * WARPS * 256 elements held in registers between the min/max pass and the quantising
+// pass (CH 16-byte chunks per thread).  WARPS = 1: a warp per unit, 8 units per 256-thread CTA, nothing
+// but shuffles shared.  WARPS > 1: a CTA of WARPS warps per unit, one barrier to join their extremes.
+template <int CH, int WARPS>
+__global__ void __launch_bounds__(WARPS == 1 ? 256 : WARPS * 32) quant_contig_reg_kernel(
+    const __half *__restrict__ x, long long n_units, float rel,
+    uint8_t *__restrict__ codes, void *__restrict__ min_int, int min_bytes, __half *__restrict__ scale,
+    unsigned long long *__restrict__ ghist, int *__restrict__ status) {
+    constexpr int NT = WARPS == 1 ? 256 : WARPS * 32;       // threads per CTA
+    constexpr int GT = WARPS * 32;                          // threads per unit
+    constexpr long long ULEN = (long long)CH * GT * 8;
+    __shared__ unsigned int shist[(NT / 32) * 256];
+    __shared__ float red[2][WARPS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gt = WARPS == 1 ? lane : tid;                 // index inside the unit
+    if (ghist) hist_clear(shist, tid, NT);
+    int flags = 0;
+    const long long u_step = WARPS == 1 ? (long long)gridDim.x * 8 : (long long)gridDim.x;
+    // every thread of the CTA runs the same number of rounds (the barrier below), units past the end idle
+    for (long long u0 = WARPS == 1 ? (long long)blockIdx.x * 8 : (long long)blockIdx.x; u0 < n_units; u0 += u_step) {
+    const long long u = WARPS == 1 ? u0 + warp : u0;
+    const bool active = u < n_units;
+    const __half *xu = x + u * ULEN;
+    uint4 v[CH];
+    float mn = INFINITY, mx = -INFINITY;
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < CH; i++) v[i] = *reinterpret_cast<const uint4 *>(xu + (long long)(i * GT + gt) * 8);
+#pragma unroll
+        for (int i = 0; i < CH; i++) minmax8(v[i], mn, mx);
+    }
+    mn = -kvc_warp_max(-mn); mx = kvc_warp_max(mx);
+    if (WARPS > 1) {
+        if (lane == 0) { red[0][warp] = mn; red[1][warp] = mx; }
+        __syncthreads();
+        mn = red[0][0]; mx = red[1][0];
+#pragma unroll
+        for (int w = 1; w < WARPS; w++) { mn = fminf(mn, red[0][w]); mx = fmaxf(mx, red[1][w]); }
+    }
+    if (active) {
+        __half sc;
+        const UnitParam p = unit_param(mn, mx, rel, &sc, &flags);
+        if (gt == 0) { scale[u] = sc; store_min(min_int, min_bytes, u, p.mi, &flags); }
+#pragma unroll
+        for (int i = 0; i < CH; i++) {
+            const uint2 o = quant_eight(v[i], &p, 0, &flags, ghist ? shist + warp * 256 : nullptr);
+            *reinterpret_cast<uint2 *>(codes + u * ULEN + (long long)(i * GT + gt) * 8) = o;
+        }
+    }
+    if (WARPS > 1) __syncthreads();                         // the extremes are read before the next unit's
+    }
+    if (flags) atomicOr(status, flags);
+    if (ghist) hist_flush(shist, ghist, tid, NT);
 }
 
 // ---- BlockQuant: one unit per token block (x sequence), far larger than a CTA ------------------
@@ -230,18 +302,18 @@ __global__ void __launch_bounds__(256) quant_block_apply_kernel(
     const __half *__restrict__ x, long long B, long long row_len, int blk, int batch_shared,
     const unsigned int *__restrict__ ws, uint8_t *__restrict__ codes,
     unsigned long long *__restrict__ ghist, int *__restrict__ status) {
-    __shared__ unsigned int shist[256];
+    __shared__ unsigned int shist[8 * 256];
     const int tid = threadIdx.x;
     const long long row = blockIdx.x, t = row / B, b = row % B;
     const long long u = batch_shared ? t / blk : (t / blk) * B + b;
-    if (ghist) { for (int i = tid; i < 256; i += 256) shist[i] = 0; __syncthreads(); }
+    if (ghist) hist_clear(shist, tid, 256);
     UnitParam p;
     p.sf = __uint_as_float(ws[2 * u]); p.mi = __uint_as_float(ws[2 * u + 1]);
     p.rcp = (p.sf == 0.0f || p.sf != p.sf) ? 0.0f : __frcp_rn(p.sf);
     int flags = 0;
     for (long long k = tid; k < row_len / 8; k += 256) {
         uint4 v = *reinterpret_cast<const uint4 *>(x + row * row_len + k * 8);
-        uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist : nullptr);
+        uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist + (tid >> 5) * 256 : nullptr);
         *reinterpret_cast<uint2 *>(codes + row * row_len + k * 8) = o;
     }
     if (flags) atomicOr(status, flags);
@@ -350,6 +422,19 @@ extern "C" int kvc_quantize(const void *x, int64_t T, int64_t B, int64_t H, int6
     case KVC_MODE_VECTOR: {
         long long ulen = mode == KVC_MODE_VECTOR ? D : (batch_shared ? B * H * D : H * D);
         long long n_units = T * B * H * D / ulen;
+#define KVC_QR(CH_, W_) quant_contig_reg_kernel<CH_, W_><<<(unsigned)std::min<long long>((W_) == 1 ? (n_units + 7) / 8 : n_units, (long long)kvc_sm_count() * (2048 / ((W_) == 1 ? 256 : (W_) * 32))), (W_) == 1 ? 256 : (W_) * 32, 0, s>>>( \
+        xh, n_units, rel, codes, min_int, min_bytes, sc, hist, status)
+        if (n_units < (1ll << 31) && (ulen == 256 || ulen == 512 || ulen == 1024 || ulen == 2048 || ulen == 4096 || ulen == 8192)) {
+            switch (ulen) {
+            case 256: KVC_QR(1, 1); break;
+            case 512: KVC_QR(2, 1); break;
+            case 1024: KVC_QR(4, 1); break;
+            case 2048: KVC_QR(4, 2); break;
+            case 4096: KVC_QR(4, 4); break;
+            default: KVC_QR(4, 8); break;
+            }
+        } else
+#undef KVC_QR
         if (ulen >= 2048) {
             KVC_REQUIRE(n_units < (1ll << 31), "kvc_quantize: too many units");
             quant_contig_kernel<256><<<(unsigned)n_units, 256, 0, s>>>(xh, n_units, ulen, rel, codes, min_int, min_bytes, sc, hist, status);
