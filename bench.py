@@ -210,10 +210,10 @@ def run_codec(args, rank, world, local):
                     book = ops.build_codebook(hist)
                     total, st2 = ops.encode(codes, is_k, book.encode_table(), bi, ti, enc)
                     ev[1].record()
-                    n = int(total[0].item())
+                    n, maxb = (int(x) for x in total.tolist())
                     flags = ops.read_status(st, False) | ops.read_status(st2, False)
                     ev[2].record()
-                    back, st3 = ops.decode(enc[:n], bi, ti, book, T, B, H, is_k)
+                    back, st3 = ops.decode(enc[:n], bi, ti, book, T, B, H, is_k, max_block=maxb)
                     ev[3].record()
                     torch.cuda.synchronize()
                     if flags & 0x20:            # a block beyond 8191 bytes: the format's u16 fields cannot hold it

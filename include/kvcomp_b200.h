@@ -173,6 +173,12 @@ int kvc_encode(const uint8_t *codes, int64_t T, int64_t cols, int is_k,
 int kvc_decode(const uint8_t *encoded, int64_t encoded_bytes, const void *block_info,
                const uint16_t *thread_info, const void *book, int64_t T, int64_t cols, int is_k,
                uint8_t *codes, int32_t *status, kvc_stream_t stream);
+/* kvc_decode with the stream's largest block size (kvc_encode's total_bytes[1]; 0 = unknown, the
+ * format's 8191): smaller staging slots let more CTAs share an SM.  A block beyond the bound is
+ * skipped and flagged KVC_FLAG_BAD_STREAM. */
+int kvc_decode_bounded(const uint8_t *encoded, int64_t encoded_bytes, const void *block_info,
+                       const uint16_t *thread_info, const void *book, int64_t T, int64_t cols, int is_k,
+                       uint32_t max_block_bytes, uint8_t *codes, int32_t *status, kvc_stream_t stream);
 
 /* k_decode_and_mat_vec_mul_cuda_export (kernels.cu:1093-1136): raw scores
  * S[b,hq,t] = sum_c x^K[t,b,hkv,c] * q[b,hq,c], fp32 accumulation.  q: device fp16

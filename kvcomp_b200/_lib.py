@@ -65,6 +65,7 @@ _SIGNATURES = {
     "kvc_encode_workspace": (_i64, [_i64, _i64, _i32]),
     "kvc_encode": (_i32, [_vp, _i64, _i64, _i32, _vp, _i32, _u32, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp]),
     "kvc_decode": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp]),
+    "kvc_decode_bounded": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _u32, _vp, _vp, _vp]),
     "kvc_fused_qk": (_i32, [C.POINTER(Cache), _i64, _i64, _i64, _i64, _vp, _vp, _i32, _vp, _vp]),
     "kvc_fused_pv": (_i32, [C.POINTER(Cache), _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "kvc_attn_workspace": (_i64, [_i64, _i64, _i32]),

@@ -200,7 +200,8 @@ class KVCompCtx:
         old = None
         if self.compressed_ctx_len:
             old, st = ops.decode(self._enc.used(), self._bi.used(), self._ti.used(), self.book,
-                                 self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k)
+                                 self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k,
+                                 max_block=self.max_block_bytes)
             ops.read_status(st, what="entropy_decode")
         hist = ops.histogram(new_codes.view(-1))
         if old is not None:
@@ -247,7 +248,8 @@ class KVCompCtx:
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         out, st = ops.decode(self._enc.used(), self._bi.used(), self._ti.used(), self.book,
-                             self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k)
+                             self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k,
+                             max_block=self.max_block_bytes)
         stop.record()
         stop.synchronize()
         ops.read_status(st, what="entropy_decode")

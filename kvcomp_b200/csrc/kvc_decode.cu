@@ -10,18 +10,19 @@ namespace {
 constexpr int SLOT_BYTES = 8192 + 32;      // a block is at most 8191 bytes (u16 fields) + alignment lead
 constexpr int TILE_STRIDE = 136;          // 128 symbols + KVC_DECODE_OVERRUN + 2 of padding, a multiple of 4
 
-struct DecodeSmem {
+struct DecodeSmem {                         // followed by 4 staging slots (sized at launch), then the 4 tiles
     KvcBookSmem book;
-    uint8_t slot[4][SLOT_BYTES];
-    uint8_t tile[4][64 * TILE_STRIDE];      // also the padding a corrupt stream's overrun reads land in
 };
+constexpr int TILE_BYTES = 64 * TILE_STRIDE; // a tile; the tiles are also the padding a corrupt stream's overrun reads land in
 
 __global__ void __launch_bounds__(256) decode_kernel(
     const uint8_t *__restrict__ encoded, long long encoded_bytes, const uint2 *__restrict__ block_info,
     const uint16_t *__restrict__ thread_info, const void *__restrict__ book, long long nblk, long long cols, int is_k,
-    uint8_t *__restrict__ codes, int *__restrict__ status) {
+    uint32_t max_block, uint32_t slot_bytes, uint8_t *__restrict__ codes, int *__restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     DecodeSmem &sm = *reinterpret_cast<DecodeSmem *>(smem_raw);
+    uint8_t *const slots = smem_raw + sizeof(DecodeSmem), *const tiles = slots + 4 * slot_bytes;
+    const bool esc = reinterpret_cast<const kvc_book_header *>(book)->max_len > KVC_LUT_BITS;   // uniform over the grid
     const int tid = threadIdx.x, sub = tid >> 6, v = tid & 63;      // sub-block and vector of this thread
     const long long row = cols * 128;
     kvc_load_book(sm.book, book, tid, 256);
@@ -34,28 +35,29 @@ __global__ void __launch_bounds__(256) decode_kernel(
         if (active) {
             const uint2 bi = block_info[blk];
             nbytes = bi.y & 0xffffu;
-            if (nbytes > 8191u || (long long)bi.x + nbytes > encoded_bytes) { nbytes = 0; flags |= KVC_FLAG_BAD_STREAM; }
-            lead = kvc_stage_block(sm.slot[sub], encoded, encoded_bytes, bi.x, nbytes, v, 64);
+            if (nbytes > max_block || (long long)bi.x + nbytes > encoded_bytes) { nbytes = 0; flags |= KVC_FLAG_BAD_STREAM; }
+            lead = kvc_stage_block(slots + sub * slot_bytes, encoded, encoded_bytes, bi.x, nbytes, v, 64);
         }
         __syncthreads();
         if (active && nbytes) {
             const uint32_t start = v ? (uint32_t)(thread_info[blk * 64 + v - 1] >> 3) : 0u;
-            uint8_t *trow = sm.tile[sub] + v * TILE_STRIDE;
+            uint8_t *trow = tiles + sub * TILE_BYTES + v * TILE_STRIDE;
             bool ok = start < nbytes;
-            if (ok)
-                ok = kvc_decode_vector<true, 0>(kvc_smem_addr(sm.slot[sub]), lead + start, kvc_smem_addr(sm.book.lut),
-                                             kvc_smem_addr(sm.book.tree), 0u,
-                                             [&](uint32_t e, uint32_t c) {
-                                                 // three byte stores; bytes past the lookup's symbols are rewritten
-                                                 // by the next lookup, bytes past position 127 land in the row padding
-                                                 uint8_t *d = trow + c;
-                                                 d[0] = (uint8_t)(e >> 8); d[1] = (uint8_t)(e >> 16); d[2] = (uint8_t)(e >> 24);
-                                             });
+            // three byte stores per lookup; bytes past the lookup's symbols are rewritten by the next
+            // lookup, bytes past position 127 land in the row padding
+            auto put = [&](uint32_t e, uint32_t c) {
+                uint8_t *d = trow + c;
+                d[0] = (uint8_t)(e >> 8); d[1] = (uint8_t)(e >> 16); d[2] = (uint8_t)(e >> 24);
+            };
+            const uint32_t slot_s = kvc_smem_addr(slots + sub * slot_bytes), lut_s = kvc_smem_addr(sm.book.lut),
+                           tree_s = kvc_smem_addr(sm.book.tree);
+            if (ok) ok = esc ? kvc_decode_vector<true, 0>(slot_s, lead + start, lut_s, tree_s, 0u, put)
+                             : kvc_decode_vector<false, 0>(slot_s, lead + start, lut_s, tree_s, 0u, put);
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
         }
         __syncthreads();
         if (active && nbytes) {
-            const uint8_t *tile = sm.tile[sub];
+            const uint8_t *tile = tiles + sub * TILE_BYTES;
             if (is_k) {
                 const long long j = blk / cols, col = blk % cols;
                 uint8_t *dst = codes + (j * 64) * row + col * 128;
@@ -82,9 +84,9 @@ __global__ void __launch_bounds__(256) decode_kernel(
 
 }  // namespace
 
-extern "C" int kvc_decode(const uint8_t *encoded, int64_t encoded_bytes, const void *block_info,
-                          const uint16_t *thread_info, const void *book, int64_t T, int64_t cols, int is_k,
-                          uint8_t *codes, int32_t *status, kvc_stream_t stream) {
+extern "C" int kvc_decode_bounded(const uint8_t *encoded, int64_t encoded_bytes, const void *block_info,
+                                  const uint16_t *thread_info, const void *book, int64_t T, int64_t cols, int is_k,
+                                  uint32_t max_block_bytes, uint8_t *codes, int32_t *status, kvc_stream_t stream) {
     KVC_REQUIRE(encoded && block_info && thread_info && book && codes && status, "kvc_decode: null pointer");
     KVC_REQUIRE(cols > 0 && T >= 0 && encoded_bytes >= 0, "kvc_decode: bad shape");
     KVC_REQUIRE(T % (is_k ? 64 : 128) == 0, "kvc_decode: %s needs a multiple of %d tokens, got %lld",
@@ -93,15 +95,26 @@ extern "C" int kvc_decode(const uint8_t *encoded, int64_t encoded_bytes, const v
                 (reinterpret_cast<uintptr_t>(book) & 15) == 0, "kvc_decode: misaligned pointer");
     const long long nblk = is_k ? (T / 64) * cols : (T / 128) * cols * 2;
     if (nblk == 0) return KVC_OK;
-    static bool attr_set = false;
-    if (!attr_set) {
-        KVC_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecodeSmem)));
-        attr_set = true;
-    }
-    long long groups = (nblk + 3) / 4, cap = (long long)kvc_sm_count() * 3;
+    // a slot holds the largest block plus its alignment lead, in 16-byte chunks, plus the decoder's read-ahead
+    const uint32_t max_block = max_block_bytes == 0 || max_block_bytes > 8191u ? 8191u : max_block_bytes;
+    const uint32_t slot_bytes = ((max_block + 15u + 15u) & ~15u) + 16u;
+    const size_t smem = sizeof(DecodeSmem) + 4 * (size_t)slot_bytes + 4 * (size_t)TILE_BYTES;
+    KVC_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KVC_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    int occ = 0;
+    KVC_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_kernel, 256, smem));
+    KVC_REQUIRE(occ >= 1, "kvc_decode: %zu bytes of shared memory do not fit an SM", smem);
+    long long groups = (nblk + 3) / 4, cap = (long long)kvc_sm_count() * occ;
     unsigned grid = (unsigned)(groups < cap ? groups : cap);
-    decode_kernel<<<grid, 256, sizeof(DecodeSmem), kvc_cu(stream)>>>(
-        encoded, encoded_bytes, reinterpret_cast<const uint2 *>(block_info), thread_info, book, nblk, cols, is_k, codes, status);
+    decode_kernel<<<grid, 256, smem, kvc_cu(stream)>>>(
+        encoded, encoded_bytes, reinterpret_cast<const uint2 *>(block_info), thread_info, book, nblk, cols, is_k,
+        max_block, slot_bytes, codes, status);
     KVC_LAUNCH_OK();
     return KVC_OK;
+}
+
+extern "C" int kvc_decode(const uint8_t *encoded, int64_t encoded_bytes, const void *block_info,
+                          const uint16_t *thread_info, const void *book, int64_t T, int64_t cols, int is_k,
+                          uint8_t *codes, int32_t *status, kvc_stream_t stream) {
+    return kvc_decode_bounded(encoded, encoded_bytes, block_info, thread_info, book, T, cols, is_k, 0u, codes, status, stream);
 }

@@ -218,15 +218,17 @@ def encode(codes, is_k, enc_table, block_info, thread_info, encoded, base_offset
     return total, status
 
 
-def decode(encoded, block_info, thread_info, book, T, B, H, is_k, out=None, status=None):
+def decode(encoded, block_info, thread_info, book, T, B, H, is_k, out=None, status=None, max_block=0):
+    """Huffman-decode a stream to its uint8 codes [T,B,H,128].  max_block: the stream's largest block in
+    bytes as the encoder reported it (0 = unknown); a known bound lets more CTAs share an SM."""
     lib = _lib.load()
     _cuda(encoded, torch.uint8, "encoded")
     dev = encoded.device
     out = torch.empty((T, B, H, 128), dtype=torch.uint8, device=dev) if out is None else _cuda(out, torch.uint8, "out")
     status = new_status(dev) if status is None else status
     with torch.cuda.device(dev):
-        _lib.check(lib.kvc_decode(_p(encoded), encoded.numel(), _p(block_info), _p(thread_info), _p(book.blob),
-                                  T, B * H, int(is_k), _p(out), _p(status), _stream()), "kvc_decode")
+        _lib.check(lib.kvc_decode_bounded(_p(encoded), encoded.numel(), _p(block_info), _p(thread_info), _p(book.blob),
+                                          T, B * H, int(is_k), int(max_block), _p(out), _p(status), _stream()), "kvc_decode")
     return out, status
 
 
