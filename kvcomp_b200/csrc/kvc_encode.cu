@@ -155,10 +155,10 @@ __global__ void __launch_bounds__(1024) scan_blocks_kernel(const uint32_t *__res
     }
 }
 
-// Thread = vector: encode the 128 symbols at rowp into the block image `out`, starting at byte `start`.
+// Thread = vector: encode the 128 symbols held in `row` into the block image `out`, starting at byte `start`.
 // SHORT: no code is longer than 16 bits.
 template <bool SHORT>
-__device__ __forceinline__ void encode_vector(const uint32_t *rowp, const uint2 *tab, uint32_t *out, uint32_t start) {
+__device__ __forceinline__ void encode_vector(const uint32_t (&row)[32], const uint2 *tab, uint32_t *out, uint32_t start) {
     // acc collects code bits below the `have` bits it already holds; whole words leave from the top
     uint32_t wp = start >> 2, have = (start & 3u) * 8;   // the first word's leading bytes belong to the vector before
     unsigned long long acc = 0;
@@ -170,9 +170,9 @@ __device__ __forceinline__ void encode_vector(const uint32_t *rowp, const uint2 
         else out[wp] = word;
         wp++;
     };
-#pragma unroll 2
+#pragma unroll
     for (int w = 0; w < 32; w++) {
-        const uint32_t x = rowp[w];
+        const uint32_t x = row[w];
         const uint2 e0 = tab[x & 0xffu], e1 = tab[(x >> 8) & 0xffu], e2 = tab[(x >> 16) & 0xffu], e3 = tab[x >> 24];
         if (SHORT) {
             // codes of at most 16 bits: two of them make one piece of at most 32 bits, one test per pair
@@ -198,8 +198,9 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_emit_kernel(
     const uint8_t *__restrict__ codes, long long cols, int is_k, const uint32_t *__restrict__ enc, int n_entries,
     const uint16_t *__restrict__ thread_info, const uint2 *__restrict__ block_info,
     const uint32_t *__restrict__ sizes, uint32_t base_offset, uint8_t *__restrict__ encoded, long long capacity) {
-    __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE];
-    __shared__ __align__(16) uint32_t out[OUT_CAP / 4];
+    // the code tile, and after every thread has taken its row into registers, the block image
+    __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE > OUT_CAP ? 64 * TILE_STRIDE : OUT_CAP];
+    uint32_t *const out = reinterpret_cast<uint32_t *>(tile);
     __shared__ uint2 tab[256];                              // {code, length}
     __shared__ uint16_t tinfo[64];
     const int tid = threadIdx.x;
@@ -219,12 +220,16 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_emit_kernel(
     uint8_t *dst = encoded + off;
     const uint32_t lead = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15);   // image is aligned like dst
     const uint32_t end = lead + nbytes;
-    for (uint32_t i = tid; i * 16 < end + 4; i += ENC_THREADS) reinterpret_cast<uint4 *>(out)[i] = make_uint4(0u, 0u, 0u, 0u);
     const bool long_codes = __syncthreads_or(too_long) != 0;
+    uint32_t row[32];
+#pragma unroll
+    for (int w = 0; w < 32; w++) row[w] = reinterpret_cast<const uint32_t *>(tile + tid * TILE_STRIDE)[w];
+    __syncthreads();                                        // the tile is in registers: its memory becomes the image
+    for (uint32_t i = tid; i * 16 < end + 4; i += ENC_THREADS) reinterpret_cast<uint4 *>(out)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
     const uint32_t start = lead + (tid ? (uint32_t)(tinfo[tid - 1] >> 3) : 0u);
-    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(tile + tid * TILE_STRIDE);
-    if (long_codes) encode_vector<false>(rowp, tab, out, start);
-    else encode_vector<true>(rowp, tab, out, start);
+    if (long_codes) encode_vector<false>(row, tab, out, start);
+    else encode_vector<true>(row, tab, out, start);
     __syncthreads();
     // image words hold stream bytes most-significant first; swap to memory order on the way out
     uint8_t *g0 = dst - lead;                                   // 16-byte aligned
