@@ -41,7 +41,7 @@ WORKLOADS = {
 }
 
 
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.035
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.04
 
 
 def peaks():
@@ -225,7 +225,7 @@ def run_codec(args, rank, world, local):
                         comp += n + bsz + tsz + mi.numel() * 2 + sc.numel() * 2
                         orig += fp16_bytes
                         bits[name] = 8.0 * n / codes.numel()
-                        launches += 8
+                        launches += 7            # quantise, codebook, sizes, 2 scans, emit, decode
                     del codes, back, enc
                 del k, v
         if rank == 0 and rel == 0.05:
@@ -439,7 +439,8 @@ def main():
                      "bits_per_symbol": {k: float(np.mean([8.0 * a[k]["encoded"] / a[k]["symbols"] for a in accts])) for k in ("k", "v")}},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": L * B * Hq * 128 * 2,
                 "d2h_bytes_per_step": L * B * Hq * 128 * 2, "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": args.steps * L * launches_per_call,
+        # per layer: one attention kernel per chunk of query heads, then the merge of the partial results
+        "gpu_launches": args.steps * L * (launches_per_call + (1 if (splits or ops.attn_splits(T, B, Hkv)) > 1 else 0)),
         "clocks": clocks, "status_flags": flags,
     }
     # DRAM traffic of the kernel from one ncu capture (profiles/attn_decode_c1.md): read + written bytes
