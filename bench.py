@@ -428,7 +428,7 @@ def main():
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong" if heads_mode else "weak", "vs_baseline": None,
         "dtype": "u8 codes -> int32 dot products (16-bit fixed-point weights), f32 softmax, fp16 in/out", "data": "synthetic",
-        "config": {"workload": args.workload + ": " + cfg["desc"], "layers": L, "splits": splits or "balanced over the resident CTAs",
+        "config": {"workload": args.workload + ": " + cfg["desc"], "layers": L, "splits": splits or "auto: (column, run of tiles) items drawn by the resident CTAs",
                    "l2": "inputs larger than L2 (%.2f GB of compressed cache read per step)" % (alg * L / 1e9),
                    "sharding": ("KV heads split over ranks (%d of %d query heads each), one NCCL all-gather of the outputs per step" % (Hq, Hq_total))
                    if heads_mode else "batch sequences per rank, no collective on the data path"},

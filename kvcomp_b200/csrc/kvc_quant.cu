@@ -39,13 +39,22 @@ __device__ __forceinline__ void store_min(void *min_int, int min_bytes, long lon
 // 2^-24 (relative) of the true quotient t.  x and scale carry 11 significant bits, so t is at least
 // 2^-23 (relative) away from every midpoint between two fp16 values (t = m would need m*scale = x with a
 // 12-bit m); hence q1, the correctly rounded fp32 quotient and t all round to the same fp16 value.
+// rint(v) for |v| < 2^22 without the conversion pipe: adding 1.5 * 2^23 rounds to an integer (to nearest
+// even, the mode rintf uses) and leaves that integer in the low mantissa bits.
+#define KVC_RINT_MAGIC 12582912.0f
 __device__ __forceinline__ uint32_t quant_one(__half x, const UnitParam &p, int *flags) {
     if (p.sf == 0.0f || p.sf != p.sf) return 0u;
     const float xf = __half2float(x);
     const float q0 = __fmul_rn(xf, p.rcp);
     const float q1 = __fmaf_rn(__fmaf_rn(-q0, p.sf, xf), p.rcp, q0);
-    float q = rintf(__half2float(__float2half_rn(q1)));
-    float c = __half2float(__float2half_rn(__fsub_rn(q, p.mi)));
+    const float qh = __half2float(__float2half_rn(q1));                      // |qh| <= 65504 (or inf)
+    const float q = __fsub_rn(__fadd_rn(qh, KVC_RINT_MAGIC), KVC_RINT_MAGIC);  // = rintf(qh) for finite qh
+    const float d = __fsub_rn(q, p.mi);
+    if (d >= 0.0f && d <= 255.0f)            // an integer that fp16 holds exactly: the code, read from the mantissa
+        return (uint32_t)__float_as_int(__fadd_rn(d, KVC_RINT_MAGIC)) & 0xffu;
+    // out of range (or not finite): follow the fp16 arithmetic to the end, as the reference's tensors do
+    const float qs = rintf(qh);
+    const float c = __half2float(__float2half_rn(__fsub_rn(qs, p.mi)));
     if (!(c >= 0.0f && c <= 255.0f)) { *flags |= KVC_FLAG_CODE_OVERFLOW; }
     return (uint32_t)(int)c & 0xffu;
 }
