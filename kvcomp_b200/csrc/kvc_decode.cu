@@ -8,7 +8,7 @@
 namespace {
 
 constexpr int SLOT_BYTES = 8192 + 32;      // a block is at most 8191 bytes (u16 fields) + alignment lead
-constexpr int TILE_STRIDE = 136;          // 128 symbols + KVC_DECODE_OVERRUN + 2 of padding, a multiple of 4
+constexpr int TILE_STRIDE = 132;          // 128 symbols + a word for the decoder's overrun; 33 words keep column reads off one bank
 
 struct DecodeSmem {                         // followed by 4 staging slots (sized at launch), then the 4 tiles
     KvcBookSmem book;
@@ -43,16 +43,21 @@ __global__ void __launch_bounds__(256) decode_kernel(
             const uint32_t start = v ? (uint32_t)(thread_info[blk * 64 + v - 1] >> 3) : 0u;
             uint8_t *trow = tiles + sub * TILE_BYTES + v * TILE_STRIDE;
             bool ok = start < nbytes;
-            // three byte stores per lookup; bytes past the lookup's symbols are rewritten by the next
-            // lookup, bytes past position 127 land in the row padding
-            auto put = [&](uint32_t e, uint32_t c) {
-                uint8_t *d = trow + c;
-                d[0] = (uint8_t)(e >> 8); d[1] = (uint8_t)(e >> 16); d[2] = (uint8_t)(e >> 24);
+            // the symbols of the lookups collect in a register pair and leave as whole words; symbols
+            // past position 127 (at most KVC_DECODE_OVERRUN) land in the row's padding word
+            unsigned long long buf = 0;
+            uint32_t fill = 0;                               // bytes held in buf, < 4 between lookups
+            uint32_t *wrow = reinterpret_cast<uint32_t *>(trow);
+            auto put = [&](uint32_t e, uint32_t) {
+                buf |= (unsigned long long)(e >> 8) << (fill * 8);
+                fill += (e >> 6) & 3u;
+                if (fill >= 4u) { *wrow++ = (uint32_t)buf; buf >>= 32; fill -= 4u; }
             };
             const uint32_t slot_s = kvc_smem_addr(slots + sub * slot_bytes), lut_s = kvc_smem_addr(sm.book.lut),
                            tree_s = kvc_smem_addr(sm.book.tree);
             if (ok) ok = esc ? kvc_decode_vector<true, 0>(slot_s, lead + start, lut_s, tree_s, 0u, put)
                              : kvc_decode_vector<false, 0>(slot_s, lead + start, lut_s, tree_s, 0u, put);
+            if (ok && wrow < reinterpret_cast<uint32_t *>(trow) + TILE_STRIDE / 4) *wrow = (uint32_t)buf;
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
         }
         __syncthreads();

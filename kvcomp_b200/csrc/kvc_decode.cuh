@@ -104,7 +104,7 @@ __device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
 // The decoder state is (position << 6) | bit offset into the (hi, lo) register pair, so applying a
 // table entry is one add of its low byte.
 // emit(e, a): `e` holds up to three symbols in bytes 1..3 for positions c..c+2 of the vector (unused
-// bytes are 0; byte 0 is the table entry's advance byte and must be ignored); a = (base + c) << SHIFT:
+// bytes are 0; byte 0 is the table entry's advance byte: its bits 6-7 count the symbols); a = (base + c) << SHIFT:
 // the position counter starts at `base`, so a consumer that keeps one record of 2^SHIFT bytes per
 // position at shared address A passes base = A >> SHIFT and gets the record's address with no add.
 // The end of the vector is tested once per KVC_DECODE_UNROLL lookups, so emit may be handed symbols for
@@ -148,7 +148,7 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
                 node = (nd >> (16 * bit)) & 0xffffu;
             }
             ok = ok && found;
-            emit(sym << 8, a);
+            emit((sym << 8) | (1u << 6), a);                          // advance byte: one symbol
             state += 1u << 6;
         }
         if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
