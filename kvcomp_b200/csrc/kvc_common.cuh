@@ -77,6 +77,14 @@ __device__ __forceinline__ float kvc_scale_value(unsigned short bits) { return _
 
 __device__ __forceinline__ uint32_t kvc_bswap(uint32_t x) { return __byte_perm(x, 0, 0x0123); }
 
+// 4x4 byte transpose: in a, b, c, d = rows; out a = {a0,b0,c0,d0}, b = {a1,b1,c1,d1}, ...
+__device__ __forceinline__ void kvc_transpose4x4(uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
+    const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+    const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+    a = __byte_perm(t0, t1, 0x5410); b = __byte_perm(t0, t1, 0x7632);
+    c = __byte_perm(t2, t3, 0x5410); d = __byte_perm(t2, t3, 0x7632);
+}
+
 __device__ __forceinline__ float kvc_warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

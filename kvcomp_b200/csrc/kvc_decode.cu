@@ -74,12 +74,17 @@ __global__ void __launch_bounds__(256) decode_kernel(
             } else {
                 const long long g = blk / (cols * 2), m = blk % (cols * 2);
                 uint8_t *dst = codes + (g * 128) * row + m * 64;
-                for (int i = v; i < 128 * 16; i += 64) {
-                    int t = i >> 4, w = i & 15;
-                    uint32_t x = 0;
-#pragma unroll
-                    for (int k = 0; k < 4; k++) x |= (uint32_t)tile[(w * 4 + k) * TILE_STRIDE + t] << (8 * k);
-                    *reinterpret_cast<uint32_t *>(dst + t * row + w * 4) = x;
+                for (int i = v; i < 32 * 16; i += 64) {     // 32 groups of 4 tokens x 16 words of 4 channels
+                    const int tg = i >> 4, w = i & 15;
+                    uint32_t x0 = *reinterpret_cast<const uint32_t *>(tile + (w * 4 + 0) * TILE_STRIDE + tg * 4);
+                    uint32_t x1 = *reinterpret_cast<const uint32_t *>(tile + (w * 4 + 1) * TILE_STRIDE + tg * 4);
+                    uint32_t x2 = *reinterpret_cast<const uint32_t *>(tile + (w * 4 + 2) * TILE_STRIDE + tg * 4);
+                    uint32_t x3 = *reinterpret_cast<const uint32_t *>(tile + (w * 4 + 3) * TILE_STRIDE + tg * 4);
+                    kvc_transpose4x4(x0, x1, x2, x3);          // now one word per token: its 4 channels
+                    *reinterpret_cast<uint32_t *>(dst + (tg * 4 + 0) * row + w * 4) = x0;
+                    *reinterpret_cast<uint32_t *>(dst + (tg * 4 + 1) * row + w * 4) = x1;
+                    *reinterpret_cast<uint32_t *>(dst + (tg * 4 + 2) * row + w * 4) = x2;
+                    *reinterpret_cast<uint32_t *>(dst + (tg * 4 + 3) * row + w * 4) = x3;
                 }
             }
         }

@@ -35,12 +35,18 @@ __device__ __forceinline__ void stage_tile(uint8_t *tile, const uint8_t *__restr
     } else {
         const long long g = blk / (cols * 2), m = blk % (cols * 2);
         const uint8_t *src = codes + (g * 128) * row + m * 64;
-#pragma unroll 8
-        for (int i = tid; i < 128 * 16; i += ENC_THREADS) {    // 128 token rows x 16 words
-            int t = i >> 4, w = i & 15;
-            uint32_t x = *reinterpret_cast<const uint32_t *>(src + t * row + w * 4);
-#pragma unroll
-            for (int k = 0; k < 4; k++) tile[(w * 4 + k) * TILE_STRIDE + t] = (uint8_t)(x >> (8 * k));
+#pragma unroll 2
+        for (int i = tid; i < 32 * 16; i += ENC_THREADS) {     // 32 groups of 4 token rows x 16 words of 4 channels
+            const int tg = i >> 4, w = i & 15;
+            uint32_t x0 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 0) * row + w * 4);
+            uint32_t x1 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 1) * row + w * 4);
+            uint32_t x2 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 2) * row + w * 4);
+            uint32_t x3 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 3) * row + w * 4);
+            kvc_transpose4x4(x0, x1, x2, x3);                  // now one word per channel: its 4 tokens
+            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 0) * TILE_STRIDE + tg * 4) = x0;
+            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 1) * TILE_STRIDE + tg * 4) = x1;
+            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 2) * TILE_STRIDE + tg * 4) = x2;
+            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 3) * TILE_STRIDE + tg * 4) = x3;
         }
     }
 }
