@@ -35,7 +35,6 @@ namespace {
 
 constexpr int SLOT_BYTES = 8192 + 32;     // a block is at most 8191 bytes (u16 fields) + alignment lead
 constexpr int SLOT_PAD = 1024;           // readable bytes behind the last staging slot
-constexpr int WROW = 136;                 // weight words per vector: 128 positions + zeroed overrun (>= 128 + KVC_DECODE_OVERRUN + 1)
 constexpr int NTHR = 256;
 constexpr int ATTN_PART_FLOATS = 4 + 256;   // a partial result of the attention kernel: m, l, two unused, acc[2][128]
 
@@ -76,6 +75,61 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
+}
+
+// ---- grouped queries (G >= 2): decode first, multiply afterwards -----------------------------------
+// With several query heads per KV head the weight records of a position grow to 16 or 32 bytes, and
+// 32 lanes at 32 different positions fetch 0.5-1 KB per lookup: the kernel becomes bound by shared-memory
+// wavefronts.  So a thread first decodes its vector into a private row of bytes in shared memory and
+// then walks the row four positions at a time; now all lanes of a warp are at the same position, the
+// weight words are one broadcast read, and they need no overlapping window: a word holds the hi (or lo)
+// bytes of 4 consecutive positions.  The integer sums are the same as in the one-pass form.
+constexpr int ROW_STRIDE = 132;           // bytes of a thread's row: 128 symbols + a word of overrun; 33 words spread the banks
+constexpr int WROW = 136;                 // weight words per vector of the one-pass form: 128 positions + zeroed overrun (>= 128 + KVC_DECODE_OVERRUN + 1)
+template <int G, bool ROWS> struct VecWords { static constexpr int value = ROWS ? 32 * 2 * G : 2 * WROW * G; };   // weight words of one vector
+
+// {hi word, lo word} of 4 consecutive positions (byte i = position i)
+__device__ __forceinline__ uint2 pack4_dense(int q0, int q1, int q2, int q3) {
+    uint2 r;
+    r.x = ((uint32_t)(q0 >> 8) & 0xffu) | (((uint32_t)(q1 >> 8) & 0xffu) << 8) | (((uint32_t)(q2 >> 8) & 0xffu) << 16) | (((uint32_t)(q3 >> 8) & 0xffu) << 24);
+    r.y = ((uint32_t)q0 & 0xffu) | (((uint32_t)q1 & 0xffu) << 8) | (((uint32_t)q2 & 0xffu) << 16) | (((uint32_t)q3 & 0xffu) << 24);
+    return r;
+}
+
+// decode the thread's vector into `row` (its own 33 words), then dot it with the weight words at w:
+// [32 groups of 4 positions][hi | lo][G]
+template <int G>
+__device__ __forceinline__ bool decode_rows(const uint8_t *slot, uint32_t byte_pos, const KvcBookSmem &book, bool esc,
+                                            uint32_t *row, const uint32_t *w, int (&hi)[G], int (&lo)[G]) {
+    static_assert(G == 2 || G == 4, "two or four query heads");
+    const uint32_t slot_s = kvc_smem_addr(slot), lut_s = kvc_smem_addr(book.lut), tree_s = kvc_smem_addr(book.tree);
+    unsigned long long buf = 0;
+    uint32_t fill = 0, *wr = row;                            // bytes held in buf, < 4 between lookups
+    auto put = [&](uint32_t e, uint32_t) {
+        buf |= (unsigned long long)(e >> 8) << (fill * 8);
+        fill += (e >> 6) & 3u;
+        if (fill >= 4u) { *wr++ = (uint32_t)buf; buf >>= 32; fill -= 4u; }
+    };
+    const bool ok = esc ? kvc_decode_vector<true, 0>(slot_s, byte_pos, lut_s, tree_s, 0u, put)
+                        : kvc_decode_vector<false, 0>(slot_s, byte_pos, lut_s, tree_s, 0u, put);
+    if (wr < row + ROW_STRIDE / 4) *wr = (uint32_t)buf;      // symbols past position 127 end up in the 33rd word
+    const uint32_t row_s = kvc_smem_addr(row), w_s = kvc_smem_addr(w);
+#pragma unroll 8
+    for (int wg = 0; wg < 32; wg++) {
+        const uint32_t x = kvc_lds32(row_s + wg * 4);
+        if (G == 4) {
+            const uint4 a = lds128(w_s + wg * 32), b = lds128(w_s + wg * 32 + 16);
+            hi[0] = kvc_dp4a_us(x, a.x, hi[0]); lo[0] = kvc_dp4a_uu(x, b.x, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(x, a.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(x, b.y, lo[1 % G]);
+            hi[2 % G] = kvc_dp4a_us(x, a.z, hi[2 % G]); lo[2 % G] = kvc_dp4a_uu(x, b.z, lo[2 % G]);
+            hi[3 % G] = kvc_dp4a_us(x, a.w, hi[3 % G]); lo[3 % G] = kvc_dp4a_uu(x, b.w, lo[3 % G]);
+        } else {
+            const uint4 a = lds128(w_s + wg * 16);
+            hi[0] = kvc_dp4a_us(x, a.x, hi[0]); lo[0] = kvc_dp4a_uu(x, a.z, lo[0]);
+            hi[1 % G] = kvc_dp4a_us(x, a.y, hi[1 % G]); lo[1 % G] = kvc_dp4a_uu(x, a.w, lo[1 % G]);
+        }
+    }
+    return ok;
 }
 
 // Where the hi / lo weight word of position c and head g sits in a vector's 2 * WROW * G words.  One or
@@ -197,7 +251,8 @@ __device__ __forceinline__ void k_units_load(KUnit &u, const kvc_qmeta_dev &m, l
     }
 }
 
-template <int G>
+// ROWS: the layout of decode_rows (grouped queries in the attention kernel) instead of w_hi / w_lo
+template <int G, bool ROWS = false>
 __device__ __forceinline__ void k_weights_build(uint32_t *w, float *step, float *zp, const float *qf, const KUnit &u,
                                                 bool channel_units, long long tok0, long long T, int tid) {
     const int lane = tid & 31, wp = tid >> 5, sub = wp & 3;
@@ -222,18 +277,23 @@ __device__ __forceinline__ void k_weights_build(uint32_t *w, float *step, float 
         int q4[7];
 #pragma unroll
         for (int i = 0; i < 4; i++) q4[i] = __float2int_rn(wv[i] * inv);
+        uint32_t *row = w + (size_t)sub * VecWords<G, ROWS>::value;
+        if (ROWS) {                                             // the lane's 4 positions are one group: [group][hi | lo][g]
+            const uint2 r = pack4_dense(q4[0], q4[1], q4[2], q4[3]);
+            row[(lane * 2 + 0) * G + g] = r.x; row[(lane * 2 + 1) * G + g] = r.y;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 3; i++) {                           // the next lane's first three values
-            int nv = __shfl_down_sync(0xffffffffu, q4[i], 1);
-            q4[4 + i] = lane == 31 ? 0 : nv;
-        }
-        uint32_t *row = w + (size_t)sub * 2 * WROW * G;           // layout: w_hi / w_lo
+            for (int i = 0; i < 3; i++) {                       // the next lane's first three values
+                int nv = __shfl_down_sync(0xffffffffu, q4[i], 1);
+                q4[4 + i] = lane == 31 ? 0 : nv;
+            }
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const uint2 r = pack4(q4[i], q4[i + 1], q4[i + 2], q4[i + 3]);
-            row[w_hi<G>(lane * 4 + i, g)] = r.x; row[w_lo<G>(lane * 4 + i, g)] = r.y;
+            for (int i = 0; i < 4; i++) {                       // layout: w_hi / w_lo
+                const uint2 r = pack4(q4[i], q4[i + 1], q4[i + 2], q4[i + 3]);
+                row[w_hi<G>(lane * 4 + i, g)] = r.x; row[w_lo<G>(lane * 4 + i, g)] = r.y;
+            }
+            if (lane < WROW - 128) { row[w_hi<G>(128 + lane, g)] = 0u; row[w_lo<G>(128 + lane, g)] = 0u; }
         }
-        if (lane < WROW - 128) { row[w_hi<G>(128 + lane, g)] = 0u; row[w_lo<G>(128 + lane, g)] = 0u; }
         if (lane == 0) { step[sub * G + g] = st; zp[sub * G + g] = z; }
     }
 }
@@ -295,7 +355,7 @@ __device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], cons
 // Called by all 256 threads (thread = token of the tile, grp = its 128-token group, tl = its index in
 // the group) with wv[g] = p[g] * scale of the token.  Builds records ps[grp][tl][hi|lo][g], step[grp][g].
 // `red` is scratch for 8*G floats, `q16` for 2*G*(128+4) int16.  Contains three block barriers.
-template <int G>
+template <int G, bool ROWS = false>
 __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red, int16_t *q16, const float (&wv)[G],
                                           int tid) {
     const int lane = tid & 31, warp = tid >> 5, grp = tid >> 7, tl = tid & 127;
@@ -315,10 +375,17 @@ __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const int16_t *qq = q16 + (grp * G + g) * 132 + tl;
-        uint32_t *row = ps + (size_t)grp * 2 * WROW * G;          // layout: w_hi / w_lo
-        const uint2 r = pack4(qq[0], qq[1], qq[2], qq[3]);
-        row[w_hi<G>(tl, g)] = r.x; row[w_lo<G>(tl, g)] = r.y;
-        if (tl < WROW - 128) { row[w_hi<G>(128 + tl, g)] = 0u; row[w_lo<G>(128 + tl, g)] = 0u; }
+        uint32_t *row = ps + (size_t)grp * VecWords<G, ROWS>::value;
+        if (ROWS) {                                             // [group of 4 tokens][hi | lo][g]
+            if ((tl & 3) == 0) {
+                const uint2 r = pack4_dense(qq[0], qq[1], qq[2], qq[3]);
+                row[((tl >> 2) * 2 + 0) * G + g] = r.x; row[((tl >> 2) * 2 + 1) * G + g] = r.y;
+            }
+        } else {                                                // layout: w_hi / w_lo
+            const uint2 r = pack4(qq[0], qq[1], qq[2], qq[3]);
+            row[w_hi<G>(tl, g)] = r.x; row[w_lo<G>(tl, g)] = r.y;
+            if (tl < WROW - 128) { row[w_hi<G>(128 + tl, g)] = 0u; row[w_lo<G>(128 + tl, g)] = 0u; }
+        }
     }
     __syncthreads();
 }
@@ -440,10 +507,10 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
 
 // ---- one-pass decode attention -------------------------------------------------------------------
 template <int G>
-struct alignas(32) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch) and
+struct alignas(32) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch),
     KvcBookSmem bookK, bookV;         // SLOT_PAD bytes that a corrupt stream's decoder overrun may read
-    alignas(32) uint32_t w[4 * 2 * WROW * G];     // K weight records; reused for the tail and the final cross-group sum
-    alignas(32) uint32_t ps[2 * 2 * WROW * G];    // V weight records
+    alignas(32) uint32_t w[4 * VecWords<G, (G >= 2)>::value];     // K weight words; reused for the tail and the final cross-group sum
+    alignas(32) uint32_t ps[2 * VecWords<G, (G >= 2)>::value];    // V weight words
     float kstep[4 * G], zp[4 * G];
     float vstep[2 * G];
     float qf[G * 128];
@@ -477,6 +544,8 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     extern __shared__ __align__(128) uint8_t smem_raw[];
     AttnSmem<G> &sm = *reinterpret_cast<AttnSmem<G> *>(smem_raw);
     uint8_t *const slotsK = smem_raw + sizeof(AttnSmem<G>), *const slotsV = slotsK + 4 * p.slotK_bytes;
+    constexpr bool ROWS = G >= 2;                          // grouped queries: decode into rows, multiply afterwards
+    uint32_t *const myrow = reinterpret_cast<uint32_t *>(slotsV + 4 * p.slotV_bytes + SLOT_PAD) + threadIdx.x * (ROW_STRIDE / 4);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
     const int grp = tid >> 7, ch = tid & 127;
     const long long T = p.T, B = p.B, Hkv = p.Hkv, Hq = p.Hq;
@@ -599,7 +668,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
             if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
         }
-        k_weights_build<G>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, tok0, T, tid);
+        k_weights_build<G, ROWS>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, tok0, T, tid);
         if (BULK && !kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
         __syncthreads();
         // ---- K: scores of this tile's tokens
@@ -609,7 +678,10 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okK[sub];
-            if (ok) ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, sm.w + sub * 2 * WROW * G, hi, lo);
+            if (ok) {
+                if constexpr (ROWS) ok = decode_rows<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, myrow, sm.w + sub * VecWords<G, true>::value, hi, lo);
+                else ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, sm.w + sub * VecWords<G, false>::value, hi, lo);
+            }
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
             k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km.sc != 0, kvc_scale_value(cur.ksc), (float)cur.kmi);
         } else {
@@ -636,7 +708,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * (float)cur.vmi);
             if (lane == 0) { sm.red[1][warp * G + g] = ssum; sm.red[2][warp * G + g] = zsum; }
         }
-        v_weights<G>(sm.ps, sm.vstep, sm.red[3], sm.q16, wv, tid);      // three barriers inside
+        v_weights<G, ROWS>(sm.ps, sm.vstep, sm.red[3], sm.q16, wv, tid);      // three barriers inside
 #pragma unroll
         for (int g = 0; g < G; g++) {
             float lt = 0.f;
@@ -654,7 +726,10 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
             bool ok = sm.okV[sub];
-            if (ok) ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, sm.ps + grp * 2 * WROW * G, hi, lo);
+            if (ok) {
+                if constexpr (ROWS) ok = decode_rows<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, myrow, sm.ps + grp * VecWords<G, true>::value, hi, lo);
+                else ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, sm.ps + grp * VecWords<G, false>::value, hi, lo);
+            }
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
 #pragma unroll
             for (int g = 0; g < G; g++)
@@ -945,7 +1020,7 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
         p.g0 = g0;
 #define KVC_AT(GG, BB)                                                                                          \
     {                                                                                                           \
-        const size_t smem = slot_total + sizeof(AttnSmem<GG>);                                                  \
+        const size_t smem = slot_total + sizeof(AttnSmem<GG>) + ((GG) >= 2 ? NTHR * ROW_STRIDE : 0);               \
         if (int rc = set_smem(attn_decode_kernel<GG, BB>, smem)) return rc;                                     \
         int occ = 0;                                                                                            \
         KVC_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, attn_decode_kernel<GG, BB>, NTHR, smem)); \
