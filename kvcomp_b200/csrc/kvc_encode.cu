@@ -23,30 +23,50 @@ constexpr int ENC_THREADS = 64;                   // one thread per vector of th
 __device__ __forceinline__ void stage_tile(uint8_t *tile, const uint8_t *__restrict__ codes, long long blk,
                                            long long cols, int is_k, int tid) {
     const long long row = cols * 128;
+    // K: 16-byte loads, all of a thread's 8 in flight at once (rows are 128 bytes at 16-byte aligned
+    // offsets of a 4-byte aligned base: the base decides whether the wide load is legal)
+    const bool wide = (reinterpret_cast<uintptr_t>(codes) & 15) == 0;
     if (is_k) {
         const long long j = blk / cols, col = blk % cols;
         const uint8_t *src = codes + (j * 64) * row + col * 128;
+        if (wide) {
+            uint4 x[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {                       // 64 rows x 8 chunks of 16 bytes
+                const int i = tid + k * ENC_THREADS, v = i >> 3, c = i & 7;
+                x[k] = *reinterpret_cast<const uint4 *>(src + v * row + c * 16);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int i = tid + k * ENC_THREADS, v = i >> 3, c = i & 7;
+                uint32_t *d = reinterpret_cast<uint32_t *>(tile + v * TILE_STRIDE + c * 16);
+                d[0] = x[k].x; d[1] = x[k].y; d[2] = x[k].z; d[3] = x[k].w;
+            }
+        } else {
 #pragma unroll 8
-        for (int i = tid; i < 64 * 32; i += ENC_THREADS) {     // 64 rows x 32 words
-            int v = i >> 5, w = i & 31;
-            uint32_t x = *reinterpret_cast<const uint32_t *>(src + v * row + w * 4);
-            *reinterpret_cast<uint32_t *>(tile + v * TILE_STRIDE + w * 4) = x;
+            for (int i = tid; i < 64 * 32; i += ENC_THREADS) {  // 64 rows x 32 words
+                int v = i >> 5, w = i & 31;
+                uint32_t x = *reinterpret_cast<const uint32_t *>(src + v * row + w * 4);
+                *reinterpret_cast<uint32_t *>(tile + v * TILE_STRIDE + w * 4) = x;
+            }
         }
     } else {
         const long long g = blk / (cols * 2), m = blk % (cols * 2);
         const uint8_t *src = codes + (g * 128) * row + m * 64;
+        {   // 4-byte loads: 16 lanes cover a token row's 64 bytes, and the transposed stores meet no bank twice
 #pragma unroll 2
-        for (int i = tid; i < 32 * 16; i += ENC_THREADS) {     // 32 groups of 4 token rows x 16 words of 4 channels
-            const int tg = i >> 4, w = i & 15;
-            uint32_t x0 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 0) * row + w * 4);
-            uint32_t x1 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 1) * row + w * 4);
-            uint32_t x2 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 2) * row + w * 4);
-            uint32_t x3 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 3) * row + w * 4);
-            kvc_transpose4x4(x0, x1, x2, x3);                  // now one word per channel: its 4 tokens
-            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 0) * TILE_STRIDE + tg * 4) = x0;
-            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 1) * TILE_STRIDE + tg * 4) = x1;
-            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 2) * TILE_STRIDE + tg * 4) = x2;
-            *reinterpret_cast<uint32_t *>(tile + (w * 4 + 3) * TILE_STRIDE + tg * 4) = x3;
+            for (int i = tid; i < 32 * 16; i += ENC_THREADS) {  // 32 groups of 4 token rows x 16 words of 4 channels
+                const int tg = i >> 4, w = i & 15;
+                uint32_t x0 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 0) * row + w * 4);
+                uint32_t x1 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 1) * row + w * 4);
+                uint32_t x2 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 2) * row + w * 4);
+                uint32_t x3 = *reinterpret_cast<const uint32_t *>(src + (tg * 4 + 3) * row + w * 4);
+                kvc_transpose4x4(x0, x1, x2, x3);               // now one word per channel: its 4 tokens
+                *reinterpret_cast<uint32_t *>(tile + (w * 4 + 0) * TILE_STRIDE + tg * 4) = x0;
+                *reinterpret_cast<uint32_t *>(tile + (w * 4 + 1) * TILE_STRIDE + tg * 4) = x1;
+                *reinterpret_cast<uint32_t *>(tile + (w * 4 + 2) * TILE_STRIDE + tg * 4) = x2;
+                *reinterpret_cast<uint32_t *>(tile + (w * 4 + 3) * TILE_STRIDE + tg * 4) = x3;
+            }
         }
     }
 }
