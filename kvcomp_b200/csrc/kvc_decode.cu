@@ -66,10 +66,19 @@ __global__ void __launch_bounds__(256) decode_kernel(
             if (is_k) {
                 const long long j = blk / cols, col = blk % cols;
                 uint8_t *dst = codes + (j * 64) * row + col * 128;
-                for (int i = v; i < 64 * 32; i += 64) {
-                    int r = i >> 5, w = i & 31;
-                    *reinterpret_cast<uint32_t *>(dst + r * row + w * 4) =
-                        *reinterpret_cast<const uint32_t *>(tile + r * TILE_STRIDE + w * 4);
+                if ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) {
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {            // 64 rows x 8 chunks of 16 bytes
+                        const int i = v + k * 64, r = i >> 3, c = i & 7;
+                        const uint32_t *t4 = reinterpret_cast<const uint32_t *>(tile + r * TILE_STRIDE + c * 16);
+                        *reinterpret_cast<uint4 *>(dst + r * row + c * 16) = make_uint4(t4[0], t4[1], t4[2], t4[3]);
+                    }
+                } else {
+                    for (int i = v; i < 64 * 32; i += 64) {
+                        int r = i >> 5, w = i & 31;
+                        *reinterpret_cast<uint32_t *>(dst + r * row + w * 4) =
+                            *reinterpret_cast<const uint32_t *>(tile + r * TILE_STRIDE + w * 4);
+                    }
                 }
             } else {
                 const long long g = blk / (cols * 2), m = blk % (cols * 2);
