@@ -89,10 +89,14 @@ __device__ __forceinline__ void hist_flush(const unsigned int *sh, unsigned long
     }
 }
 
+// extremes of 8 halves: packed fp16 min / max (exact, a NaN operand yields the other one, as fminf does),
+// widened once at the end
 __device__ __forceinline__ void minmax8(const uint4 &v, float &mn, float &mx) {
-    const __half *h = reinterpret_cast<const __half *>(&v);
-#pragma unroll
-    for (int i = 0; i < 8; i++) { float f = __half2float(h[i]); mn = fminf(mn, f); mx = fmaxf(mx, f); }
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    const __half2 lo = __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]));
+    const __half2 hi = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    mn = fminf(mn, fminf(__low2float(lo), __high2float(lo)));
+    mx = fmaxf(mx, fmaxf(__low2float(hi), __high2float(hi)));
 }
 
 // ---- ChannelQuant (utils/compute.py:140): one unit per (token block, b, h, channel) -------------
@@ -111,17 +115,20 @@ __global__ void __launch_bounds__(128) quant_channel_kernel(
     const long long tile = blockIdx.x;                 // (j * B + b) * H + h
     const long long h = tile % H, b = (tile / H) % B, j = tile / (H * B);
     const long long base = ((j * blk) * B + b) * H * 128 + h * 128 + cg * 8;
-    float mn[8], mx[8];
+    __half2 mn2[4], mx2[4];                                 // extremes of the thread's 8 channels, two per register
 #pragma unroll
-    for (int i = 0; i < 8; i++) { mn[i] = INFINITY; mx[i] = -INFINITY; }
+    for (int i = 0; i < 4; i++) { mn2[i] = __float2half2_rn(INFINITY); mx2[i] = __float2half2_rn(-INFINITY); }
     for (int i = r; i < blk; i += 8) {
         uint4 v = *reinterpret_cast<const uint4 *>(x + base + i * row_stride);
-        const __half *hv = reinterpret_cast<const __half *>(&v);
+        const __half2 *hv = reinterpret_cast<const __half2 *>(&v);
 #pragma unroll
-        for (int k = 0; k < 8; k++) { float f = __half2float(hv[k]); mn[k] = fminf(mn[k], f); mx[k] = fmaxf(mx[k], f); }
+        for (int k = 0; k < 4; k++) { mn2[k] = __hmin2(mn2[k], hv[k]); mx2[k] = __hmax2(mx2[k], hv[k]); }
     }
 #pragma unroll
-    for (int k = 0; k < 8; k++) { smn[r][cg * 8 + k] = mn[k]; smx[r][cg * 8 + k] = mx[k]; }
+    for (int k = 0; k < 4; k++) {
+        smn[r][cg * 8 + 2 * k] = __low2float(mn2[k]); smn[r][cg * 8 + 2 * k + 1] = __high2float(mn2[k]);
+        smx[r][cg * 8 + 2 * k] = __low2float(mx2[k]); smx[r][cg * 8 + 2 * k + 1] = __high2float(mx2[k]);
+    }
     __syncthreads();
     {   // thread = channel: fold the 8 partials, derive the unit's parameters once, share them
         float a = smn[0][tid], z = smx[0][tid];
