@@ -66,6 +66,21 @@ def test_quantize_bit_exact(ops, which, mode, block, rel, shared):
     assert np.array_equal(xh.view(np.uint16), orc.dequant(codes, mi, sc, m).view(np.uint16))
 
 
+@pytest.mark.parametrize("H,shared", [(2, False), (3, False), (16, False), (24, False), (32, False), (64, False), (8, True)])
+def test_quantize_token_units_of_every_size(ops, H, shared):
+    """Token units of 256 .. 8192 elements take the register-resident kernels (1, 2, 4 or 8 warps per
+    unit), other lengths the generic one: same bits from all of them."""
+    k, v, _ = synth(64, 2, H, seed=5)
+    codes, mi, sc, m, _ = orc.quant(v, orc.MODE_TOKEN, 128, 0.07, shared)
+    hist = torch.zeros(256, dtype=torch.int64, device="cuda")
+    c2, mi2, sc2, spec, st = ops.quantize(dev(v), orc.MODE_TOKEN, 128, 0.07, shared, min_dtype=torch.int16, hist=hist)
+    assert ops.read_status(st) & 0x4 == 0
+    assert np.array_equal(sc2.cpu().numpy().view(np.uint16), sc.view(np.uint16))
+    assert np.array_equal(mi2.cpu().numpy(), mi)
+    assert np.array_equal(c2.cpu().numpy(), codes)
+    assert np.array_equal(hist.cpu().numpy(), orc.histogram(codes))
+
+
 def test_quantize_matches_reference_golden(ops, golden_dir):
     z = np.load(os.path.join(golden_dir, "quant_golden.npz"))
     meta = json.loads(bytes(z["cases_json"]).decode())
@@ -183,6 +198,36 @@ def test_encode_decode_bit_exact(ops, is_k, mode, rel, T, B, H):
     # a stream written by the checker decodes on the GPU too
     out2, st = ops.decode(dev(odata), dev(obi), dev(oti.view(np.int16)), r["book"], T, B, H, is_k)
     assert ops.read_status(st) == 0 and np.array_equal(out2.cpu().numpy(), codes)
+
+
+@pytest.mark.parametrize("is_k", [True, False])
+def test_codec_buffers_off_16_byte_boundaries(ops, is_k):
+    """Codes that do not start on 16 bytes are staged with 4-byte loads and written back with 4-byte
+    stores; a bound on the block size changes nothing but the launch; a bound that is too small is
+    reported, not overrun."""
+    T, B, H = 256, 2, 3
+    k, v, _ = synth(T, B, H, seed=19)
+    x = k if is_k else v
+    r = _pipeline(ops, x, is_k, orc.MODE_CHANNEL if is_k else orc.MODE_TOKEN, 64 if is_k else 128, 0.05, False)
+    n = T * B * H * 128
+    shifted = torch.zeros(n + 32, dtype=torch.uint8, device="cuda")
+    codes4 = shifted[4:4 + n].view(T, B, H, 128)
+    codes4.copy_(r["codes"])
+    bsz, tsz, _, cap = ops.buffer_sizes(T, B * H * 128, is_k)
+    bi = torch.zeros(bsz, dtype=torch.uint8, device="cuda")
+    ti = torch.zeros(tsz // 2, dtype=torch.int16, device="cuda")
+    enc = torch.zeros(cap, dtype=torch.uint8, device="cuda")
+    total, st = ops.encode(codes4, is_k, r["book"].encode_table(), bi, ti, enc)
+    assert ops.read_status(st) & ~0x10 == 0 and int(total[0]) == r["n"]
+    assert torch.equal(enc[:r["n"]], r["enc"][:r["n"]]) and torch.equal(bi, r["bi"]) and torch.equal(ti, r["ti"])
+    out_buf = torch.zeros(n + 32, dtype=torch.uint8, device="cuda")
+    out4 = out_buf[4:4 + n].view(T, B, H, 128)
+    for bound in (0, r["maxb"], 8191):
+        out4.zero_()
+        _, st = ops.decode(r["enc"][:r["n"]], r["bi"], r["ti"], r["book"], T, B, H, is_k, out=out4, max_block=bound)
+        assert ops.read_status(st) == 0 and torch.equal(out4, r["codes"])
+    _, st = ops.decode(r["enc"][:r["n"]], r["bi"], r["ti"], r["book"], T, B, H, is_k, max_block=r["maxb"] - 1)
+    assert ops.read_status(st, False) & 0x80           # KVC_FLAG_BAD_STREAM
 
 
 def test_encode_base_offset_and_append(ops):
