@@ -118,13 +118,13 @@ struct BookSmem {
     short left[512], right[512];
     uint32_t enc_code[256], enc_len[256];
     uint32_t tree[512];          // wide tree: lo16 = child0 (or LEAF), hi16 = child1 (or symbol)
+    long long count[256];        // the histogram, fetched by all threads at once
     int n_nodes, n_symbols, min_sym, max_sym, max_len, flags;
 };
 
 // insert every code into the decode trees in ascending symbol order
 // (build_decode_code_book, src/huffman.cpp:229-252); run by one thread
-__device__ void build_trees(BookSmem &s) {
-    for (int i = 0; i < 512; i++) s.tree[i] = KVC_TREE_NONE | (KVC_TREE_NONE << 16);
+__device__ void build_trees(BookSmem &s) {      // s.tree was cleared to {NONE, NONE} by the whole CTA
     int n = 2;
     for (int sym = 0; sym < 256; sym++) {
         int len = (int)s.enc_len[sym];
@@ -211,13 +211,15 @@ __global__ void __launch_bounds__(256) build_codebook_kernel(const unsigned long
     __shared__ BookSmem s;
     const int tid = threadIdx.x;
     s.enc_code[tid] = 0; s.enc_len[tid] = 0;
+    s.count[tid] = (long long)hist[tid];                    // one coalesced load instead of 256 dependent ones
+    s.tree[tid] = s.tree[tid + 256] = KVC_TREE_NONE | (KVC_TREE_NONE << 16);
     __syncthreads();
     if (tid == 0) {
         Heap hp; hp.f = s.hf; hp.id = s.hid; hp.n = 0;
         int nsym = 0, mn = 256, mx = -1;
         s.flags = 0;
         for (int i = 0; i < 256; i++) {
-            long long c = (long long)hist[i];
+            long long c = s.count[i];
             if (c > 0) { heap_push(hp, c, (short)i); nsym++; if (i < mn) mn = i; mx = i; }
         }
         s.n_symbols = nsym; s.min_sym = nsym ? mn : 0; s.max_sym = nsym ? mx : 0; s.max_len = 0;
@@ -266,6 +268,7 @@ __global__ void __launch_bounds__(256) book_from_tree_kernel(const uint8_t *__re
     __shared__ BookSmem s;
     const int tid = threadIdx.x;
     s.enc_code[tid] = 0; s.enc_len[tid] = 0;
+    s.tree[tid] = s.tree[tid + 256] = KVC_TREE_NONE | (KVC_TREE_NONE << 16);
     __syncthreads();
     if (tid == 0) {
         s.flags = 0; s.max_len = 0;
