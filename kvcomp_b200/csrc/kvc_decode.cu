@@ -7,7 +7,6 @@
 
 namespace {
 
-constexpr int SLOT_BYTES = 8192 + 32;      // a block is at most 8191 bytes (u16 fields) + alignment lead
 constexpr int TILE_STRIDE = 132;          // 128 symbols + a word for the decoder's overrun; 33 words keep column reads off one bank
 
 struct DecodeSmem {                         // followed by 4 staging slots (sized at launch), then the 4 tiles
