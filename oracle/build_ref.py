@@ -1,8 +1,8 @@
 """Compile the reference's own host codec (src/huffman.cpp, src/utils.cpp) as a CPU-only
 torch extension into oracle/_ref/ -- a checker for the C restatement, never product code.
 
-The sources are compiled where they lie under the reference tree (default /root/reference,
-override with REF=...); nothing is copied.  The reference's own build system is not run:
+The sources are compiled where they lie under the reference tree (REF=/path/to/reference);
+nothing is copied.  The reference's own build system is not run:
 its setup.py also compiles the CUDA kernels, which this checker does not need.
 """
 import os

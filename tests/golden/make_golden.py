@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this folder from the reference itself.
 
-Run once in a container that has the reference tree (default /root/reference):
+Run once where the reference tree is at hand (REF=/path/to/reference):
 
     python tests/golden/make_golden.py
 

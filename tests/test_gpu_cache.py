@@ -1,7 +1,7 @@
 """GPU tests of the reference-facing layers: the `kvcomp_cuda` operator module and the cache classes
 (KVCompCtx, KVCompCache), written the way the reference's own scripts exercise them
 (kvcomp_cuda_extension/scripts/test_py_ctx_k_2d_load.py, test_py_ctx_v.py, twice_get.py,
-accuracy/reproduce_cuda_error.py), with the CPU checker as the judge."""
+accuracy/reproduce_cuda_error.py), with the CPU checker as the referee."""
 import math
 
 import numpy as np
