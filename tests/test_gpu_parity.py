@@ -358,6 +358,10 @@ ATTN_CASES = [  # kmode, vmode, shared, T, B, Hkv, Hq, Tr, splits, min_dtype
     (orc.MODE_BLOCK, orc.MODE_TOKEN, True, 384, 2, 2, 2, 100, 1, torch.int8),
     (orc.MODE_CHANNEL, orc.MODE_TOKEN, False, 896, 1, 2, 12, 300, 2, torch.int16),
     (orc.MODE_CHANNEL, orc.MODE_VECTOR, False, 128, 3, 1, 1, 1, 0, torch.int16),
+    (orc.MODE_CHANNEL, orc.MODE_TOKEN, False, 1152, 3, 5, 15, 0, 0, torch.int16),     # 3 query heads per KV head: chunks of 2 + 1
+    (orc.MODE_BLOCK, orc.MODE_TOKEN, False, 256, 1, 7, 35, 37, 9, torch.int16),       # 5 per KV head (4 + 1), more splits than tiles
+    (orc.MODE_CHANNEL, orc.MODE_TOKEN, False, 2304, 1, 2, 4, 0, 4, torch.int16),      # 2 per KV head, 9 tiles in 3 runs
+    (orc.MODE_CHANNEL, orc.MODE_TOKEN, False, 128, 2, 3, 6, 5, 0, torch.int16),       # half a tile and a tail
 ]
 
 
