@@ -105,7 +105,8 @@ typedef struct {             /* first 32 bytes of the blob */
     int32_t n_nodes;         /* nodes of the reference-format decode tree */
     int32_t flags;           /* KVC_FLAG_* raised while building */
     int32_t lut_bits;
-    int32_t reserved;
+    int32_t escape;          /* 1: some decode-table entry holds no complete code (a code longer than the
+                              * window, or bit patterns that belong to no code): decoders test for it */
 } kvc_book_header;
 
 const char *kvc_last_error(void);

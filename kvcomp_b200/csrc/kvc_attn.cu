@@ -172,7 +172,7 @@ __device__ __forceinline__ bool decode_dot(const uint8_t *slot, uint32_t byte_po
                : decode_dot_impl<G, false>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo);
 }
 __device__ __forceinline__ bool book_has_long_codes(const void *book) {
-    return reinterpret_cast<const kvc_book_header *>(book)->max_len > KVC_LUT_BITS;
+    return kvc_book_needs_escape(book);
 }
 
 // ---- staging --------------------------------------------------------------------------------------

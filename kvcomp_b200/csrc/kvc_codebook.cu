@@ -198,11 +198,17 @@ __device__ void write_book(const BookSmem &s, uint8_t *book, int tid, int nthr) 
     uint32_t *wt = reinterpret_cast<uint32_t *>(book + KVC_BOOK_OFF_TREE);
     for (int i = tid; i < 512; i += nthr) wt[i] = s.tree[i];
     uint32_t *lut = reinterpret_cast<uint32_t *>(book + KVC_BOOK_OFF_LUT);
-    for (int w = tid; w < KVC_LUT_SIZE; w += nthr) lut[w] = lut_entry(s.tree, (uint32_t)w);
+    int no_code = 0;                                        // an entry whose window holds no complete code
+    for (int w = tid; w < KVC_LUT_SIZE; w += nthr) {
+        const uint32_t e = lut_entry(s.tree, (uint32_t)w);
+        lut[w] = e;
+        no_code |= (e & 0xffu) == 0;
+    }
+    no_code = __syncthreads_or(no_code);
     if (tid == 0) {
         kvc_book_header *h = reinterpret_cast<kvc_book_header *>(book);
         h->n_symbols = s.n_symbols; h->min_sym = s.min_sym; h->max_sym = s.max_sym; h->max_len = s.max_len;
-        h->n_nodes = s.n_nodes; h->flags = s.flags; h->lut_bits = KVC_LUT_BITS; h->reserved = 0;
+        h->n_nodes = s.n_nodes; h->flags = s.flags; h->lut_bits = KVC_LUT_BITS; h->escape = no_code ? 1 : 0;
     }
 }
 

@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(256) decode_kernel(
     extern __shared__ __align__(16) uint8_t smem_raw[];
     DecodeSmem &sm = *reinterpret_cast<DecodeSmem *>(smem_raw);
     uint8_t *const slots = smem_raw + sizeof(DecodeSmem), *const tiles = slots + 4 * slot_bytes;
-    const bool esc = reinterpret_cast<const kvc_book_header *>(book)->max_len > KVC_LUT_BITS;   // uniform over the grid
+    const bool esc = kvc_book_needs_escape(book);           // uniform over the grid
     const int tid = threadIdx.x, sub = tid >> 6, v = tid & 63;      // sub-block and vector of this thread
     const long long row = cols * 128;
     kvc_load_book(sm.book, book, tid, 256);

@@ -99,6 +99,15 @@ __device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
     return v;
 }
 
+// Whether the decoder has to test every table entry for "no code ends in this window": books with a
+// code longer than the window, and books whose code is not complete (a single symbol, or a tree taken
+// from a caller's tensor with a missing branch): a corrupt stream can then show bit patterns that
+// belong to no code, and the escape-free loop would not advance on them.
+__device__ __forceinline__ bool kvc_book_needs_escape(const void *book) {
+    const kvc_book_header *h = reinterpret_cast<const kvc_book_header *>(book);
+    return h->max_len > KVC_LUT_BITS || h->escape != 0;
+}
+
 // Decode one vector.  slot_s: shared-space address of the staged block (16-byte aligned); byte_pos:
 // where the vector starts in it; lut_s / tree_s: shared-space addresses of the book's tables.
 // The decoder state is (position << 6) | bit offset into the (hi, lo) register pair, so applying a

@@ -153,7 +153,8 @@ class Book:
 
     def header(self):
         h = self.host()[:32].view(torch.int32).tolist()
-        return dict(n_symbols=h[0], min_sym=h[1], max_sym=h[2], max_len=h[3], n_nodes=h[4], flags=h[5], lut_bits=h[6])
+        return dict(n_symbols=h[0], min_sym=h[1], max_sym=h[2], max_len=h[3], n_nodes=h[4], flags=h[5], lut_bits=h[6],
+                    escape=h[7])
 
     def encode_table(self):
         """uint8 view of the 256-entry symbol-indexed {u32 code, u32 length} table (device)."""

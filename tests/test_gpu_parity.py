@@ -279,6 +279,28 @@ def test_frozen_book_flags_unseen_symbol(ops):
     assert np.array_equal(enc[:int(total[0].item())].cpu().numpy(), odata)
 
 
+def test_single_symbol_book_meets_foreign_bits(ops):
+    """A book of one symbol has the code '0' only: a 1 bit belongs to no code.  The decoders must report
+    such a stream (their table says so in the book header) and still come to an end."""
+    T, B, H = 128, 1, 2
+    codes = torch.full((T, B, H, 128), 7, dtype=torch.uint8, device="cuda")
+    book = ops.build_codebook(ops.histogram(codes.view(-1)))
+    hd = book.header()
+    assert hd["n_symbols"] == 1 and hd["max_len"] == 1 and hd["escape"] == 1
+    bsz, tsz, _, cap = ops.buffer_sizes(T, B * H * 128, True)
+    bi = torch.zeros(bsz, dtype=torch.uint8, device="cuda")
+    ti = torch.zeros(tsz // 2, dtype=torch.int16, device="cuda")
+    enc = torch.zeros(cap, dtype=torch.uint8, device="cuda")
+    total, st = ops.encode(codes, True, book.encode_table(), bi, ti, enc)
+    n = int(total[0])
+    assert ops.read_status(st) == 0 and n == T * B * H * 16          # one bit per symbol
+    out, st = ops.decode(enc[:n], bi, ti, book, T, B, H, True)
+    assert ops.read_status(st) == 0 and torch.equal(out, codes)
+    enc[5] = 0xFF; enc[n - 3] = 0x18
+    out, st = ops.decode(enc[:n], bi, ti, book, T, B, H, True)
+    assert ops.read_status(st, False) & 0x80                          # KVC_FLAG_BAD_STREAM
+
+
 def test_long_codes_use_the_slow_path(ops):
     """A very skewed alphabet has codes longer than the decode window; the stream still round-trips."""
     rng = np.random.default_rng(1)
