@@ -561,12 +561,12 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     // to arrive: CTAs that run faster (the warp schedulers favour some of an SM's CTAs) take more.
     struct Item { int col, t_lo, t_hi; };
     const bool draw = p.sched != nullptr;
-    const long long P = gridDim.x;
-    const long long w_hi = draw ? p.work : p.work * (blockIdx.x + 1) / P;
-    auto item_of = [&](long long j, Item &it) -> bool {
+    const int P = (int)gridDim.x;                           // items are counted in 32 bits (the host checks the range)
+    const int w_hi = draw ? (int)p.work : (int)(p.work * (blockIdx.x + 1) / P);
+    auto item_of = [&](int j, Item &it) -> bool {
         if (j >= w_hi) return false;
-        const int s = (int)(j % p.splits);
-        it.col = (int)(j / p.splits); it.t_lo = s * p.tiles_per_split; it.t_hi = min(n_tiles, it.t_lo + p.tiles_per_split);
+        const int s = j % p.splits;
+        it.col = j / p.splits; it.t_lo = s * p.tiles_per_split; it.t_hi = min(n_tiles, it.t_lo + p.tiles_per_split);
         return true;
     };
 
@@ -577,7 +577,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     auto validV = [&](bool on, int tile, int l) { return on && (long long)tile * 256 + (l >> 1) * 128 < T; };
 
     Item it, nit;
-    long long j_it = draw ? (long long)blockIdx.x : p.work * blockIdx.x / P, j_n1 = draw ? P + blockIdx.x : j_it + 1;
+    int j_it = draw ? (int)blockIdx.x : (int)(p.work * blockIdx.x / P), j_n1 = draw ? P + (int)blockIdx.x : j_it + 1;
     bool have = item_of(j_it, it), have_next = have && item_of(j_n1, nit);
     int drawn = 0;                                         // thread 0: the counter's answer, used an item later
     const bool any_tiles = have && it.t_lo < it.t_hi;      // items are empty only when the cache has no compressed part
@@ -825,14 +825,14 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         // ---- a partial result {m, l, -, -, acc of group 0 [128], acc of group 1 [128]}; a second kernel merges
 #pragma unroll
         for (int g = 0; g < G; g++) {
-            float *dst = p.ws_part + ((head0 + g) * p.splits + (int)(j_it % p.splits)) * ATTN_PART_FLOATS;
+            float *dst = p.ws_part + ((head0 + g) * p.splits + j_it % p.splits) * ATTN_PART_FLOATS;
             dst[4 + tid] = acc[g];                             // tid = grp * 128 + ch
             if (tid == 0) { dst[0] = m_run[g]; dst[1] = l_run[g]; }
         }
     }
     if (draw && tid == 0) sm.next_j = drawn;
     __syncthreads();                                       // the sums are read before the next column's weights overwrite them
-    const long long j_n2 = draw ? 2 * P + sm.next_j : j_n1 + 1;
+    const int j_n2 = draw ? 2 * P + sm.next_j : j_n1 + 1;
     it = nit; have = have_next; j_it = j_n1; j_n1 = j_n2;
     have_next = have && item_of(j_n1, nit);
     }   // items of the CTA

@@ -104,8 +104,7 @@ __device__ __forceinline__ uint2 kvc_lds64(uint32_t addr) {
 // from a caller's tensor with a missing branch): a corrupt stream can then show bit patterns that
 // belong to no code, and the escape-free loop would not advance on them.
 __device__ __forceinline__ bool kvc_book_needs_escape(const void *book) {
-    const kvc_book_header *h = reinterpret_cast<const kvc_book_header *>(book);
-    return h->max_len > KVC_LUT_BITS || h->escape != 0;
+    return reinterpret_cast<const kvc_book_header *>(book)->escape != 0;    // set for a code beyond the window too
 }
 
 // Decode one vector.  slot_s: shared-space address of the staged block (16-byte aligned); byte_pos:
