@@ -85,7 +85,7 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // weight words are one broadcast read, and they need no overlapping window: a word holds the hi (or lo)
 // bytes of 4 consecutive positions.  The integer sums are the same as in the one-pass form.
 constexpr int ROW_STRIDE = 132;           // bytes of a thread's row: 128 symbols + a word of overrun; 33 words spread the banks
-constexpr int WROW = 136;                 // weight words per vector of the one-pass form: 128 positions + zeroed overrun (>= 128 + KVC_DECODE_OVERRUN + 1)
+constexpr int WROW = 136;                 // weight words per vector of the one-pass form: 128 positions + zeroed overrun
 template <int G, bool ROWS> struct VecWords { static constexpr int value = ROWS ? 32 * 2 * G : 2 * WROW * G; };   // weight words of one vector
 
 // {hi word, lo word} of 4 consecutive positions (byte i = position i)
@@ -144,7 +144,7 @@ template <int G, bool ESC>
 __device__ __forceinline__ bool decode_dot_impl(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
                                                 uint32_t w_s, int (&hi)[G], int (&lo)[G]) {
     constexpr int SHIFT = G == 1 ? 3 : 4;                      // log2 of the record's bytes
-    return kvc_decode_vector<ESC, SHIFT>(slot_s, byte_pos, lut_s, tree_s, w_s >> SHIFT, [&](uint32_t syms, uint32_t a) {
+    auto emit = [&](uint32_t syms, uint32_t a) {
         if (G == 4) {
             const uint4 x = lds128(a), y = lds128(a + WROW * 16);
             hi[0] = kvc_dp4a_us(syms, x.x, hi[0]); lo[0] = kvc_dp4a_uu(syms, y.x, lo[0]);
@@ -160,7 +160,10 @@ __device__ __forceinline__ bool decode_dot_impl(uint32_t slot_s, uint32_t byte_p
             hi[0] = kvc_dp4a_us(syms, x.x, hi[0]);
             lo[0] = kvc_dp4a_uu(syms, x.y, lo[0]);
         }
-    });
+    };
+    // two lookups per round: the weight rows keep WROW - 128 zeroed positions for what is emitted past 127
+    static_assert(WROW >= 128 + KVC_DECODE_OVERRUN_PAIR + 1, "weight rows too short for paired lookups");
+    return kvc_decode_vector<ESC, SHIFT, decltype(emit), true>(slot_s, byte_pos, lut_s, tree_s, w_s >> SHIFT, emit);
 }
 // esc: the book has codes longer than the table window (uniform over the CTA)
 template <int G>

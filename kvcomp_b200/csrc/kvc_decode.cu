@@ -7,7 +7,7 @@
 
 namespace {
 
-constexpr int TILE_STRIDE = 132;          // 128 symbols + a word for the decoder's overrun; 33 words keep column reads off one bank
+constexpr int TILE_STRIDE = 140;          // 128 symbols + KVC_DECODE_OVERRUN_PAIR rounded up to words, + 1 word; 35 words keep column reads off one bank
 
 struct DecodeSmem {                         // followed by 4 staging slots (sized at launch), then the 4 tiles
     KvcBookSmem book;
@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256) decode_kernel(
             uint8_t *trow = tiles + sub * TILE_BYTES + v * TILE_STRIDE;
             bool ok = start < nbytes;
             // the symbols of the lookups collect in a register pair and leave as whole words; symbols
-            // past position 127 (at most KVC_DECODE_OVERRUN) land in the row's padding word
+            // past position 127 (at most KVC_DECODE_OVERRUN_PAIR) land in the row's padding words
             unsigned long long buf = 0;
             uint32_t fill = 0;                               // bytes held in buf, < 4 between lookups
             uint32_t *wrow = reinterpret_cast<uint32_t *>(trow);
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) decode_kernel(
             const uint32_t slot_s = kvc_smem_addr(slots + sub * slot_bytes), lut_s = kvc_smem_addr(sm.book.lut),
                            tree_s = kvc_smem_addr(sm.book.tree);
             if (ok) ok = esc ? kvc_decode_vector<true, 0>(slot_s, lead + start, lut_s, tree_s, 0u, put)
-                             : kvc_decode_vector<false, 0>(slot_s, lead + start, lut_s, tree_s, 0u, put);
+                             : kvc_decode_vector<false, 0, decltype(put), true>(slot_s, lead + start, lut_s, tree_s, 0u, put);
             if (ok && wrow < reinterpret_cast<uint32_t *>(trow) + TILE_STRIDE / 4) *wrow = (uint32_t)buf;
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
         }

@@ -12,6 +12,7 @@
 
 #define KVC_DECODE_UNROLL 1
 #define KVC_DECODE_OVERRUN (3 * KVC_DECODE_UNROLL)   // positions past 127 a decoder may emit
+#define KVC_DECODE_OVERRUN_PAIR 6                    // ... with two lookups per round (PAIR)
 
 struct KvcBookSmem {                      // per-CTA copy of the decode structures of one book
     uint32_t tree[512];
@@ -117,11 +118,12 @@ __device__ __forceinline__ bool kvc_book_needs_escape(const void *book) {
 // position at shared address A passes base = A >> SHIFT and gets the record's address with no add.
 // The end of the vector is tested once per KVC_DECODE_UNROLL lookups, so emit may be handed symbols for
 // positions up to 127 + KVC_DECODE_OVERRUN; the consumer keeps room for them (zero weights, padding).
-// ESC = false is for books whose longest code fits the table window: no escape test in the loop.
+// ESC = false is for books whose longest code fits the table window: no escape test in the loop;
+// PAIR (with ESC = false only) takes two lookups per round.
 // Every round advances by at least one symbol, so the loop ends after at most 128 rounds; a corrupt
 // stream can read at most a few hundred bytes past its vector, for which the kernels keep padding
 // behind the last slot.  Returns false when the bits do not form valid codes.
-template <bool ESC, int SHIFT, class Emit>
+template <bool ESC, int SHIFT, class Emit, bool PAIR = false>
 __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
                                                   uint32_t base, Emit emit) {
     static_assert(SHIFT >= 0 && SHIFT <= 6, "record size");
@@ -130,6 +132,27 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
     uint32_t ptr = slot_s + (byte_pos & ~3u);
     uint32_t state = (base << 6) | ((byte_pos & 3u) << 3);
     uint32_t hi = kvc_bswap(kvc_lds32(ptr)), lo = kvc_bswap(kvc_lds32(ptr + 4));
+    if (PAIR && !ESC) {
+        // Two lookups per round.  The first leaves the bit offset below 32 + KVC_LUT_BITS, so the second
+        // one's window still lies inside (hi, lo) or (lo, next word) and needs no refill in between:
+        // one refill test and one end test per pair.  The second lookup may run although the first
+        // finished the vector, so up to KVC_DECODE_OVERRUN_PAIR positions past 127 are emitted.
+        uint32_t nx = kvc_bswap(kvc_lds32(ptr + 8));
+        ptr += 12;
+        do {
+            const uint32_t w0 = __funnelshift_l(lo, hi, state);
+            const uint32_t e0 = kvc_lds32(lut_s + ((w0 >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
+            emit(e0, (state >> (6 - SHIFT)) & AMASK);
+            state = (uint32_t)kvc_dp4a_uu(e0, 1u, (int)state);
+            const bool up = (state & 32u) != 0;
+            const uint32_t w1 = __funnelshift_l(up ? nx : lo, up ? lo : hi, state);
+            const uint32_t e1 = kvc_lds32(lut_s + ((w1 >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
+            emit(e1, (state >> (6 - SHIFT)) & AMASK);
+            state = (uint32_t)kvc_dp4a_uu(e1, 1u, (int)state);
+            if (state & 32u) { hi = lo; lo = nx; nx = kvc_bswap(kvc_lds32(ptr)); ptr += 4; state -= 32u; }
+        } while (state < end);
+        return true;
+    }
     uint32_t nxt = kvc_lds32(ptr + 8);     // one word of read-ahead keeps the refill off the critical path
     ptr += 12;
     bool ok = true;
