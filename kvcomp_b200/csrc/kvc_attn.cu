@@ -103,16 +103,16 @@ __device__ __forceinline__ bool decode_rows(const uint8_t *slot, uint32_t byte_p
                                             uint32_t *row, const uint32_t *w, int (&hi)[G], int (&lo)[G]) {
     static_assert(G == 2 || G == 4, "two or four query heads");
     const uint32_t slot_s = kvc_smem_addr(slot), lut_s = kvc_smem_addr(book.lut), tree_s = kvc_smem_addr(book.tree);
-    unsigned long long buf = 0;
-    uint32_t fill = 0, *wr = row;                            // bytes held in buf, < 4 between lookups
-    auto put = [&](uint32_t e, uint32_t) {
-        buf |= (unsigned long long)(e >> 8) << (fill * 8);
-        fill += (e >> 6) & 3u;
-        if (fill >= 4u) { *wr++ = (uint32_t)buf; buf >>= 32; fill -= 4u; }
+    const uint32_t row_s0 = kvc_smem_addr(row);
+    // three byte stores per lookup at the position the decoder hands out (its counter starts at the
+    // row's address); bytes past the lookup's symbols are rewritten by the next lookup, bytes past
+    // position 127 land in the row's 33rd word
+    auto put = [&](uint32_t e, uint32_t a) {
+        asm volatile("st.shared.u8 [%0], %1;\n\tst.shared.u8 [%0+1], %2;\n\tst.shared.u8 [%0+2], %3;"
+                     :: "r"(a), "r"(e >> 8), "r"(e >> 16), "r"(e >> 24) : "memory");
     };
-    const bool ok = esc ? kvc_decode_vector<true, 0>(slot_s, byte_pos, lut_s, tree_s, 0u, put)
-                        : kvc_decode_vector<false, 0>(slot_s, byte_pos, lut_s, tree_s, 0u, put);
-    if (wr < row + ROW_STRIDE / 4) *wr = (uint32_t)buf;      // symbols past position 127 end up in the 33rd word
+    const bool ok = esc ? kvc_decode_vector<true, 0>(slot_s, byte_pos, lut_s, tree_s, row_s0, put)
+                        : kvc_decode_vector<false, 0>(slot_s, byte_pos, lut_s, tree_s, row_s0, put);
     const uint32_t row_s = kvc_smem_addr(row), w_s = kvc_smem_addr(w);
 #pragma unroll 8
     for (int wg = 0; wg < 32; wg++) {
