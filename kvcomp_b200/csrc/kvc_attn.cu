@@ -84,7 +84,8 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // then walks the row four positions at a time; now all lanes of a warp are at the same position, the
 // weight words are one broadcast read, and they need no overlapping window: a word holds the hi (or lo)
 // bytes of 4 consecutive positions.  The integer sums are the same as in the one-pass form.
-constexpr int ROW_STRIDE = 132;           // bytes of a thread's row: 128 symbols + a word of overrun; 33 words spread the banks
+constexpr int ROW_STRIDE = 140;           // bytes of a thread's row: 128 symbols + up to 8 of overrun, + 1 word; 35 words spread the banks
+static_assert(ROW_STRIDE >= 128 + KVC_DECODE_OVERRUN_PAIR + 3, "rows too short for paired lookups");
 constexpr int WROW = 136;                 // weight words per vector of the one-pass form: 128 positions + zeroed overrun
 template <int G, bool ROWS> struct VecWords { static constexpr int value = ROWS ? 32 * 2 * G : 2 * WROW * G; };   // weight words of one vector
 
@@ -106,13 +107,13 @@ __device__ __forceinline__ bool decode_rows(const uint8_t *slot, uint32_t byte_p
     const uint32_t row_s0 = kvc_smem_addr(row);
     // three byte stores per lookup at the position the decoder hands out (its counter starts at the
     // row's address); bytes past the lookup's symbols are rewritten by the next lookup, bytes past
-    // position 127 land in the row's 33rd word
+    // position 127 (two lookups per round: up to 8 of them) land in the row's last three words
     auto put = [&](uint32_t e, uint32_t a) {
         asm volatile("st.shared.u8 [%0], %1;\n\tst.shared.u8 [%0+1], %2;\n\tst.shared.u8 [%0+2], %3;"
                      :: "r"(a), "r"(e >> 8), "r"(e >> 16), "r"(e >> 24) : "memory");
     };
     const bool ok = esc ? kvc_decode_vector<true, 0>(slot_s, byte_pos, lut_s, tree_s, row_s0, put)
-                        : kvc_decode_vector<false, 0>(slot_s, byte_pos, lut_s, tree_s, row_s0, put);
+                        : kvc_decode_vector<false, 0, decltype(put), true>(slot_s, byte_pos, lut_s, tree_s, row_s0, put);
     const uint32_t row_s = kvc_smem_addr(row), w_s = kvc_smem_addr(w);
 #pragma unroll 8
     for (int wg = 0; wg < 32; wg++) {
@@ -512,14 +513,13 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
 template <int G>
 struct alignas(32) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch),
     KvcBookSmem bookK, bookV;         // SLOT_PAD bytes that a corrupt stream's decoder overrun may read
-    alignas(32) uint32_t w[4 * VecWords<G, (G >= 2)>::value];     // K weight words; reused for the tail and the final cross-group sum
+    alignas(32) uint32_t w[4 * VecWords<G, (G >= 2)>::value];     // K weight words; reused by v_weights (scratch), the tail and the final cross-group sum
     alignas(32) uint32_t ps[2 * VecWords<G, (G >= 2)>::value];    // V weight words
     float kstep[4 * G], zp[4 * G];
     float vstep[2 * G];
     float qf[G * 128];
     float qsum[G];
     float red[4][8 * G];              // per-warp max, sum, zpv and weight-max partials
-    int16_t q16[2 * G * 132];
     uint64_t bar[2];                  // K and V staging barriers
     uint32_t leadK[4], leadV[4];
     int okK[4], okV[4];
@@ -711,7 +711,8 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             const float ssum = kvc_warp_sum(pr), zsum = kvc_warp_sum(wv[g] * (float)cur.vmi);
             if (lane == 0) { sm.red[1][warp * G + g] = ssum; sm.red[2][warp * G + g] = zsum; }
         }
-        v_weights<G, ROWS>(sm.ps, sm.vstep, sm.red[3], sm.q16, wv, tid);      // three barriers inside
+        // (the K weights are spent: their memory is the scratch of the V weights' 16-bit values)
+        v_weights<G, ROWS>(sm.ps, sm.vstep, sm.red[3], reinterpret_cast<int16_t *>(sm.w), wv, tid);      // three barriers inside
 #pragma unroll
         for (int g = 0; g < G; g++) {
             float lt = 0.f;
