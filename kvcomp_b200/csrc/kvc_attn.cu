@@ -855,6 +855,9 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits) {
     const float *src = ws_part + (size_t)blockIdx.x * splits * ATTN_PART_FLOATS;
     const int tid = threadIdx.x;
+    // launched with programmatic stream serialisation: the CTAs may be resident before the attention
+    // kernel has finished; its partial results are complete and visible after this wait
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     float M = -CUDART_INF_F;
     for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, src[s2 * ATTN_PART_FLOATS]);
     float L = 0.f, O = 0.f;
@@ -1038,7 +1041,16 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
 #undef KVC_AT
         g0 += G;
     }
-    if (splits > 1) attn_merge_kernel<<<(unsigned)(B * Hq), 128, 0, kvc_cu(stream)>>>(p.ws_part, p.out, splits);
+    if (splits > 1) {
+        // the merge may be set up on the device while the attention kernel still runs (it waits for it)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(B * Hq)); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0; cfg.stream = kvc_cu(stream);
+        cudaLaunchAttribute attr = {};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        KVC_CUDA_OK(cudaLaunchKernelEx(&cfg, attn_merge_kernel, (const float *)p.ws_part, p.out, splits));
+    }
     KVC_LAUNCH_OK();
     return KVC_OK;
 }
