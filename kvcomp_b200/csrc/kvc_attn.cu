@@ -551,6 +551,9 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     uint32_t *const myrow = reinterpret_cast<uint32_t *>(slotsV + 4 * p.slotV_bytes + SLOT_PAD) + threadIdx.x * (ROW_STRIDE / 4);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
     const int grp = tid >> 7, ch = tid & 127;
+    // launched with programmatic stream serialisation: nothing in memory is touched before the kernel
+    // ahead of this one in the stream has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long T = p.T, B = p.B, Hkv = p.Hkv, Hq = p.Hq;
     const long long cols = B * Hkv, Gt = Hq / Hkv;
     const int n_tiles = p.n_tiles;
@@ -871,6 +874,21 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict
     out[(size_t)blockIdx.x * 128 + tid] = __float2half_rn(O / L);
 }
 
+// Launch with programmatic stream serialisation: the grid may be set up on the device while the kernel
+// ahead of it in the stream still runs.  Such a kernel starts with griddepcontrol.wait, which returns
+// when that kernel has completed and its writes are visible.
+template <class... KArgs, class... Args>
+int launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    KVC_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+    return KVC_OK;
+}
+
 template <class K>
 int set_smem(K kernel, size_t bytes) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -1034,23 +1052,16 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
         KVC_REQUIRE(occ >= 1, "kvc_attn_decode: %zu bytes of shared memory do not fit an SM", smem);             \
         long long ctas = (long long)sms * (occ < ATTN_CTAS_PER_SM ? occ : ATTN_CTAS_PER_SM);                    \
         if (ctas > p.work) ctas = p.work;                                                                       \
-        attn_decode_kernel<GG, BB><<<(unsigned)ctas, NTHR, smem, kvc_cu(stream)>>>(p);                          \
+        if (int rc = launch_overlapped(attn_decode_kernel<GG, BB>, dim3((unsigned)ctas), dim3(NTHR), smem, kvc_cu(stream), p)) return rc; \
     }
         if (bulk) { if (G == 4) KVC_AT(4, true) else if (G == 2) KVC_AT(2, true) else KVC_AT(1, true) }
         else { if (G == 4) KVC_AT(4, false) else if (G == 2) KVC_AT(2, false) else KVC_AT(1, false) }
 #undef KVC_AT
         g0 += G;
     }
-    if (splits > 1) {
-        // the merge may be set up on the device while the attention kernel still runs (it waits for it)
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(B * Hq)); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0; cfg.stream = kvc_cu(stream);
-        cudaLaunchAttribute attr = {};
-        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr.val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = &attr; cfg.numAttrs = 1;
-        KVC_CUDA_OK(cudaLaunchKernelEx(&cfg, attn_merge_kernel, (const float *)p.ws_part, p.out, splits));
-    }
+    if (splits > 1)
+        if (int rc = launch_overlapped(attn_merge_kernel, dim3((unsigned)(B * Hq)), dim3(128), 0, kvc_cu(stream),
+                                       (const float *)p.ws_part, p.out, splits)) return rc;
     KVC_LAUNCH_OK();
     return KVC_OK;
 }
