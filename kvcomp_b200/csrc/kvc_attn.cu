@@ -533,7 +533,9 @@ struct AttnParams {
     __half *out;
     float scaling;
     int n_tiles;                  // 256-token tiles per column
-    int splits, tiles_per_split;  // every column is cut into `splits` runs of `tiles_per_split` tiles
+    // every column is cut into `long_runs` runs of `tiles_per_split` tiles followed by `splits - long_runs`
+    // runs of `short_tiles` tiles; the items of the long runs of all columns come first, the short ones last
+    int splits, tiles_per_split, long_runs, short_tiles;
     long long work;               // columns * splits items
     uint32_t slotK_bytes, slotV_bytes;   // capacity of one staging slot (multiple of 16)
     float *ws_part;               // [B*Hq][splits][ATTN_PART_FLOATS]
@@ -565,14 +567,21 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     // takes the items [work*i/P, work*(i+1)/P).  With one it takes items i and P + i and draws every
     // further item from the counter, two items ahead of its use so that the answer has an item's time
     // to arrive: CTAs that run faster (the warp schedulers favour some of an SM's CTAs) take more.
-    struct Item { int col, t_lo, t_hi; };
+    struct Item { int col, t_lo, t_hi, part; };            // part: the run's index within its column
     const bool draw = p.sched != nullptr;
     const int P = (int)gridDim.x;                           // items are counted in 32 bits (the host checks the range)
     const int w_hi = draw ? (int)p.work : (int)(p.work * (blockIdx.x + 1) / P);
     auto item_of = [&](int j, Item &it) -> bool {
         if (j >= w_hi) return false;
-        const int s = j % p.splits;
-        it.col = j / p.splits; it.t_lo = s * p.tiles_per_split; it.t_hi = min(n_tiles, it.t_lo + p.tiles_per_split);
+        const int n_long = (int)cols * p.long_runs;          // items of long runs; the short runs follow: the last
+        if (j < n_long) {                                    // items to be drawn are short, so the CTAs end close together
+            const int r = j % p.long_runs;
+            it.col = j / p.long_runs; it.part = r; it.t_lo = r * p.tiles_per_split; it.t_hi = min(n_tiles, it.t_lo + p.tiles_per_split);
+        } else {
+            const int n_short = p.splits - p.long_runs, r = (j - n_long) % n_short;
+            it.col = (j - n_long) / n_short; it.part = p.long_runs + r;
+            it.t_lo = p.long_runs * p.tiles_per_split + r * p.short_tiles; it.t_hi = min(n_tiles, it.t_lo + p.short_tiles);
+        }
         return true;
     };
 
@@ -832,7 +841,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         // ---- a partial result {m, l, -, -, acc of group 0 [128], acc of group 1 [128]}; a second kernel merges
 #pragma unroll
         for (int g = 0; g < G; g++) {
-            float *dst = p.ws_part + ((head0 + g) * p.splits + j_it % p.splits) * ATTN_PART_FLOATS;
+            float *dst = p.ws_part + ((head0 + g) * p.splits + it.part) * ATTN_PART_FLOATS;
             dst[4 + tid] = acc[g];                             // tid = grp * 128 + ch
             if (tid == 0) { dst[0] = m_run[g]; dst[1] = l_run[g]; }
         }
@@ -973,15 +982,37 @@ constexpr int ATTN_CTAS_PER_SM = 3;
 // last items end close together, few enough that the per-item work (q, partial results) stays small
 constexpr int ATTN_ITEMS_PER_CTA = 4;
 
+// How the columns are cut when the caller leaves it to the library: long runs of `tps` tiles, and at the
+// end of every column short runs of half that, enough of them that each resident CTA finds about two
+// short items to finish with.  The short items are handed out last (the item order puts them behind
+// all long ones), so the CTAs of a launch end within one short item of each other.
+struct RunPlan { int tps, long_runs, short_tiles, splits; };
+static RunPlan plan_runs(long long n_tiles, long long cols, int sm_count) {
+    RunPlan r = {1, 1, 1, 1};
+    if (n_tiles <= 0 || cols <= 0) { r.tps = 0; r.long_runs = 1; r.short_tiles = 0; return r; }
+    const long long P = (long long)ATTN_CTAS_PER_SM * sm_count;
+    long long tps = cols * n_tiles / (P * ATTN_ITEMS_PER_CTA);       // tiles per long item
+    if (tps < 1) tps = 1;
+    if (tps > n_tiles) tps = n_tiles;
+    // (items of a single tile pay the per-item work too often: measured slower than no short runs at all)
+    long long short_tiles = tps >= 4 ? tps / 2 : tps;
+    long long short_region = 0;                                      // tiles of a column cut into short runs
+    if (short_tiles < tps) {
+        short_region = (2 * P * short_tiles + cols - 1) / cols;       // about two short items per CTA over all columns
+        short_region = (short_region + tps - 1) / tps * tps;
+        if (short_region > n_tiles) short_region = n_tiles;
+    }
+    long long long_runs = (n_tiles - short_region) / tps;
+    short_region = n_tiles - long_runs * tps;
+    const long long short_runs = (short_region + short_tiles - 1) / short_tiles;
+    r.tps = (int)tps; r.long_runs = (int)long_runs; r.short_tiles = (int)short_tiles; r.splits = (int)(long_runs + short_runs);
+    return r;
+}
+
 extern "C" int kvc_attn_splits(int64_t T, int64_t B, int64_t Hkv, int sm_count) {
     if (T <= 0 || B <= 0 || Hkv <= 0) return 1;
     if (sm_count <= 0) sm_count = kvc_sm_count();
-    const long long n_tiles = (T + 255) / 256, cols = B * Hkv;
-    const long long P = (long long)ATTN_CTAS_PER_SM * sm_count;
-    long long tps = cols * n_tiles / (P * ATTN_ITEMS_PER_CTA);       // tiles per item
-    if (tps < 1) tps = 1;
-    if (tps > n_tiles) tps = n_tiles;
-    return (int)((n_tiles + tps - 1) / tps);
+    return plan_runs((T + 255) / 256, B * Hkv, sm_count).splits;
 }
 
 // bytes of the zero-initialised head of a workspace: the two scheduling counters
@@ -1006,11 +1037,18 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     KVC_REQUIRE(Tr == 0 || ((reinterpret_cast<uintptr_t>(ktail) & 15) == 0), "kvc_attn_decode: ktail must be 16-byte aligned");
     const long long n_tiles = (T + 255) / 256, cols = B * Hkv;
     KVC_REQUIRE(n_tiles < (1ll << 30) && cols < (1ll << 30), "kvc_attn_decode: shape too large");
-    // every column is cut into `splits` runs of `tps` tiles; each (column, run) is one item of work
-    if (splits <= 0) splits = kvc_attn_splits(T, B, Hkv, 0);
-    if (splits > n_tiles) splits = (int)(n_tiles > 0 ? n_tiles : 1);
-    const int tps = (int)((n_tiles + splits - 1) / splits);
-    splits = tps > 0 ? (int)((n_tiles + tps - 1) / tps) : 1;
+    // every column is cut into runs of tiles; each (column, run) is one item of work.  splits > 0: that many
+    // equal runs.  Otherwise long runs and, at the end of each column, short ones (plan_runs).
+    int tps, long_runs, short_tiles;
+    if (splits <= 0) {
+        const RunPlan r = plan_runs(n_tiles, cols, kvc_sm_count());
+        tps = r.tps; long_runs = r.long_runs; short_tiles = r.short_tiles; splits = r.splits;
+    } else {
+        if (splits > n_tiles) splits = (int)(n_tiles > 0 ? n_tiles : 1);
+        tps = (int)((n_tiles + splits - 1) / splits);
+        splits = tps > 0 ? (int)((n_tiles + tps - 1) / tps) : 1;
+        long_runs = splits; short_tiles = tps;
+    }
     KVC_REQUIRE(cols * splits < (1ll << 31) - (1ll << 20), "kvc_attn_decode: too many items");
     if (splits > 1) {
         KVC_REQUIRE(workspace && workspace_bytes >= kvc_attn_workspace(B, Hq, splits),
@@ -1023,7 +1061,7 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     p.q = reinterpret_cast<const __half *>(q);
     p.ktail = reinterpret_cast<const __half *>(ktail); p.vtail = reinterpret_cast<const __half *>(vtail);
     p.out = reinterpret_cast<__half *>(out);
-    p.scaling = scaling; p.splits = splits; p.tiles_per_split = tps;
+    p.scaling = scaling; p.splits = splits; p.tiles_per_split = tps; p.long_runs = long_runs; p.short_tiles = short_tiles;
     p.n_tiles = (int)n_tiles;
     p.work = cols * splits;
     // with a workspace the CTAs draw their items from its counters (zero before the first launch, left zeroed)
