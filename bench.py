@@ -378,21 +378,39 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     flags = ops.read_status(status, what="attn_decode")
 
-    # end to end through the public call with host buffers: q comes from pinned host memory and the
-    # output goes back to pinned host memory every layer of every step (the cache itself lives in HBM)
+    # end to end through the public call with host buffers: every layer's q comes from pinned host memory
+    # and every layer's output goes back to pinned host memory, every step (the cache itself lives in HBM).
+    # The copies run on a second stream, ordered against the kernels by events: layer i+1's q arrives and
+    # layer i-1's output leaves while layer i computes.
     q_host = [q.cpu().pin_memory() for (_, _, q) in layers]
     o_host = [torch.empty((B, Hq, 128), dtype=torch.float16).pin_memory() for _ in range(L)]
     q_dev = [torch.empty_like(q) for (_, _, q) in layers]
+    copy_stream = torch.cuda.Stream(device=device)
+    q_ready = [torch.cuda.Event() for _ in range(L)]
+    o_ready = [torch.cuda.Event() for _ in range(L)]
+    step_done = torch.cuda.Event()
 
     def step_e2e():
+        main = torch.cuda.current_stream()
+        copy_stream.wait_event(step_done)               # the previous step's kernels are done with q_dev
+        with torch.cuda.stream(copy_stream):
+            for i in range(L):
+                q_dev[i].copy_(q_host[i], non_blocking=True)
+                q_ready[i].record(copy_stream)
         for i, ((caches, _, _), out) in enumerate(zip(layers, outs)):
-            q_dev[i].copy_(q_host[i], non_blocking=True)
+            main.wait_event(q_ready[i])
             ops.attn_decode(caches[0], caches[1], T, B, Hkv, q_dev[i], scaling, out=out, splits=splits, workspace=ws, status=status)
-            o_host[i].copy_(out, non_blocking=True)
+            o_ready[i].record(main)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(o_ready[i])
+                o_host[i].copy_(out, non_blocking=True)
         if heads_mode:
             dist.all_gather_into_tensor(gather_buf, out_all)
-        torch.cuda.current_stream().synchronize()       # the caller needs the result of the step
+        step_done.record(main)
+        copy_stream.synchronize()                       # the caller needs the results of the step
+        main.synchronize()
 
+    step_done.record(torch.cuda.current_stream())
     for _ in range(2):
         step_e2e()
     barrier()
