@@ -108,3 +108,21 @@ def test_bench_accounting_helpers():
     assert bench.algorithmic_bytes(acct, cfg) == 100 + 50 + 2 * (8 + 128 + 3) + 2 * cfg["B"] * cfg["Hq"] * 128 * 2
     peak, kind = bench.peaks()
     assert peak > 1000 and kind in ("measured", "fallback")
+
+
+def test_attention_run_plan_without_a_gpu():
+    """kvc_attn_splits / kvc_attn_workspace are host arithmetic (given the SM count): how many partial
+    results per head the library's own cut of the columns produces, and the bytes to hold them."""
+    from kvcomp_b200 import _lib
+    lib = _lib.load()
+    sms = 148
+    for (T, B, Hkv) in [(128, 1, 1), (1024, 1, 32), (4096, 8, 32), (32768, 16, 8), (16384, 32, 10), (131072, 1, 8)]:
+        n_tiles = (T + 255) // 256
+        parts = lib.kvc_attn_splits(T, B, Hkv, sms)
+        assert 1 <= parts <= n_tiles
+        # enough items for the CTAs the device holds, unless the cache has fewer tiles than that
+        assert parts * B * Hkv >= min(n_tiles * B * Hkv, 3 * sms) or parts == n_tiles
+        assert lib.kvc_attn_workspace(B, Hkv, parts) == 256 + (B * Hkv * parts * 260 * 4 if parts > 1 else 0)
+    assert lib.kvc_attn_splits(4096, 8, 32, sms) == 8          # runs of 2 tiles
+    assert lib.kvc_attn_splits(32768, 16, 8, sms) == 20        # 10 runs of 9 tiles, then 10 of (at most) 4
+    assert lib.kvc_attn_splits(0, 8, 32, sms) == 1
