@@ -358,15 +358,37 @@ __device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], cons
 // ---- V weights --------------------------------------------------------------------------------------
 // Called by all 256 threads (thread = token of the tile, grp = its 128-token group, tl = its index in
 // the group) with wv[g] = p[g] * scale of the token.  Builds records ps[grp][tl][hi|lo][g], step[grp][g].
-// `red` is scratch for 8*G floats, `q16` for 2*G*(128+4) int16.  Contains three block barriers.
+// `red` is scratch for 8*G floats, `q16` for 2*G*(128+4) int16 (unused with ROWS).  Contains three block
+// barriers (two with ROWS).
 template <int G, bool ROWS = false>
 __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red, int16_t *q16, const float (&wv)[G],
                                           int tid) {
     const int lane = tid & 31, warp = tid >> 5, grp = tid >> 7, tl = tid & 127;
 #pragma unroll
     for (int g = 0; g < G; g++) { float mx = kvc_warp_max(fabsf(wv[g])); if (lane == 0) red[warp * G + g] = mx; }
-    if (tl < 4) for (int g = 0; g < G; g++) q16[(grp * G + g) * 132 + 128 + tl] = 0;   // tl < 4
+    if (!ROWS && tl < 4) for (int g = 0; g < G; g++) q16[(grp * G + g) * 132 + 128 + tl] = 0;
     __syncthreads();
+    if (ROWS) {
+        // four consecutive tokens make one weight word per head: their 16-bit values reach the first of
+        // the four lanes by shuffles, no scratch and no barrier in between
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float mx = fmaxf(fmaxf(red[(grp * 4 + 0) * G + g], red[(grp * 4 + 1) * G + g]),
+                                   fmaxf(red[(grp * 4 + 2) * G + g], red[(grp * 4 + 3) * G + g]));
+            const float st = fix_step(mx);
+            const int q0 = fix_quant(wv[g], st);
+            const int q1 = __shfl_down_sync(0xffffffffu, q0, 1), q2 = __shfl_down_sync(0xffffffffu, q0, 2),
+                      q3 = __shfl_down_sync(0xffffffffu, q0, 3);
+            if (tl == 0) vstep[grp * G + g] = st;
+            if ((tl & 3) == 0) {                               // [group of 4 tokens][hi | lo][g]
+                uint32_t *row = ps + (size_t)grp * VecWords<G, ROWS>::value;
+                const uint2 r = pack4_dense(q0, q1, q2, q3);
+                row[((tl >> 2) * 2 + 0) * G + g] = r.x; row[((tl >> 2) * 2 + 1) * G + g] = r.y;
+            }
+        }
+        __syncthreads();
+        return;
+    }
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const float mx = fmaxf(fmaxf(red[(grp * 4 + 0) * G + g], red[(grp * 4 + 1) * G + g]),
@@ -379,17 +401,10 @@ __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const int16_t *qq = q16 + (grp * G + g) * 132 + tl;
-        uint32_t *row = ps + (size_t)grp * VecWords<G, ROWS>::value;
-        if (ROWS) {                                             // [group of 4 tokens][hi | lo][g]
-            if ((tl & 3) == 0) {
-                const uint2 r = pack4_dense(qq[0], qq[1], qq[2], qq[3]);
-                row[((tl >> 2) * 2 + 0) * G + g] = r.x; row[((tl >> 2) * 2 + 1) * G + g] = r.y;
-            }
-        } else {                                                // layout: w_hi / w_lo
-            const uint2 r = pack4(qq[0], qq[1], qq[2], qq[3]);
-            row[w_hi<G>(tl, g)] = r.x; row[w_lo<G>(tl, g)] = r.y;
-            if (tl < WROW - 128) { row[w_hi<G>(128 + tl, g)] = 0u; row[w_lo<G>(128 + tl, g)] = 0u; }
-        }
+        uint32_t *row = ps + (size_t)grp * VecWords<G, ROWS>::value;    // layout: w_hi / w_lo
+        const uint2 r = pack4(qq[0], qq[1], qq[2], qq[3]);
+        row[w_hi<G>(tl, g)] = r.x; row[w_lo<G>(tl, g)] = r.y;
+        if (tl < WROW - 128) { row[w_hi<G>(128 + tl, g)] = 0u; row[w_lo<G>(128 + tl, g)] = 0u; }
     }
     __syncthreads();
 }
