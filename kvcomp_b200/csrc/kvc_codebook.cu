@@ -79,37 +79,45 @@ __global__ void __launch_bounds__(256) histogram_kernel(const uint8_t *__restric
 }
 
 // ---- heap, exactly as described at the top of the file -----------------------------------------
-struct Heap { long long *f; short *id; int n; };
+// A node is one 64-bit word, (frequency << 10) | id, so that a move in the heap is one load and one
+// store; comparisons look at the frequency alone, as the reference's do (ties are decided by position).
+struct Heap { unsigned long long *w; int n; };
+__device__ __forceinline__ unsigned long long heap_word(long long f, short id) { return ((unsigned long long)f << 10) | (unsigned long long)(id & 0x3ff); }
+__device__ __forceinline__ unsigned long long heap_freq(unsigned long long w) { return w >> 10; }
 
-__device__ void heap_sift_up(Heap &hp, int hole, long long f, short id) {
+__device__ void heap_sift_up(Heap &hp, int hole, unsigned long long word) {
     while (hole > 0) {
-        int parent = (hole - 1) >> 1;
-        if (!(hp.f[parent] > f)) break;
-        hp.f[hole] = hp.f[parent]; hp.id[hole] = hp.id[parent];
+        const int parent = (hole - 1) >> 1;
+        const unsigned long long pw = hp.w[parent];
+        if (!(heap_freq(pw) > heap_freq(word))) break;
+        hp.w[hole] = pw;
         hole = parent;
     }
-    hp.f[hole] = f; hp.id[hole] = id;
+    hp.w[hole] = word;
 }
-__device__ void heap_push(Heap &hp, long long f, short id) { hp.n++; heap_sift_up(hp, hp.n - 1, f, id); }
+__device__ void heap_push(Heap &hp, long long f, short id) { hp.n++; heap_sift_up(hp, hp.n - 1, heap_word(f, id)); }
 __device__ short heap_pop(Heap &hp, long long *f_out) {
-    short top = hp.id[0]; *f_out = hp.f[0];
+    const unsigned long long top = hp.w[0];
+    *f_out = (long long)heap_freq(top);
+    const short top_id = (short)(top & 0x3ff);
     int len = --hp.n;
-    if (len == 0) return top;
-    long long vf = hp.f[len]; short vid = hp.id[len];
+    if (len == 0) return top_id;
+    const unsigned long long last = hp.w[len];
     int hole = 0, child = 0;
     while (child < (len - 1) / 2) {
         child = 2 * (child + 1);
-        if (hp.f[child] > hp.f[child - 1]) child--;
-        hp.f[hole] = hp.f[child]; hp.id[hole] = hp.id[child];
+        unsigned long long c1 = hp.w[child], c0 = hp.w[child - 1];
+        if (heap_freq(c1) > heap_freq(c0)) { child--; c1 = c0; }
+        hp.w[hole] = c1;
         hole = child;
     }
     if ((len & 1) == 0 && child == (len - 2) / 2) {
         child = 2 * (child + 1);
-        hp.f[hole] = hp.f[child - 1]; hp.id[hole] = hp.id[child - 1];
+        hp.w[hole] = hp.w[child - 1];
         hole = child - 1;
     }
-    heap_sift_up(hp, hole, vf, vid);
-    return top;
+    heap_sift_up(hp, hole, last);
+    return top_id;
 }
 
 struct BookSmem {
@@ -221,7 +229,7 @@ __global__ void __launch_bounds__(256) build_codebook_kernel(const unsigned long
     s.tree[tid] = s.tree[tid + 256] = KVC_TREE_NONE | (KVC_TREE_NONE << 16);
     __syncthreads();
     if (tid == 0) {
-        Heap hp; hp.f = s.hf; hp.id = s.hid; hp.n = 0;
+        Heap hp; hp.w = reinterpret_cast<unsigned long long *>(s.hf); hp.n = 0;
         int nsym = 0, mn = 256, mx = -1;
         s.flags = 0;
         for (int i = 0; i < 256; i++) {
@@ -231,7 +239,8 @@ __global__ void __launch_bounds__(256) build_codebook_kernel(const unsigned long
         s.n_symbols = nsym; s.min_sym = nsym ? mn : 0; s.max_sym = nsym ? mx : 0; s.max_len = 0;
         if (nsym == 0) s.flags |= KVC_FLAG_NO_SYMBOLS;
         else if (nsym == 1) {          // utils/huffman.py:42-44: the lone symbol gets '0'
-            s.enc_code[hp.id[0]] = 0; s.enc_len[hp.id[0]] = 1; s.max_len = 1;
+            const int lone = (int)(hp.w[0] & 0x3ff);
+            s.enc_code[lone] = 0; s.enc_len[lone] = 1; s.max_len = 1;
         } else {
             short next = 256;
             while (hp.n > 1) {
@@ -245,7 +254,7 @@ __global__ void __launch_bounds__(256) build_codebook_kernel(const unsigned long
             // iterative walk; the heap arrays are free now and serve as the stack
             short *st_node = s.hid; long long *st_code = s.hf;     // code | (len << 40)
             int sp = 1;
-            st_node[0] = hp.id[0]; st_code[0] = 0;
+            st_node[0] = (short)(hp.w[0] & 0x3ff); st_code[0] = 0;
             while (sp) {
                 sp--;
                 short nd = st_node[sp];
