@@ -5,9 +5,9 @@
 //              per vector sums its code lengths, a two-warp scan -> thread_info, block byte count
 //   B  scan    exclusive prefix sum of block byte counts -> block_info offsets (ascending id)
 //   C  emit    one 64-thread CTA per block: a thread per vector shifts its codes through a 64-bit
-//              register and writes whole words into a shared-memory image of the block that is
-//              aligned like its destination (only the first and last word of a vector, which it
-//              may share with its neighbours, are OR-ed in); the image goes out as 128-bit stores
+//              register and ORs whole words into a zeroed shared-memory image of the block that is
+//              aligned like its destination (a vector shares its first and last word with its
+//              neighbours); the image goes out as 128-bit stores
 #include "kvc_common.cuh"
 
 namespace {
@@ -188,13 +188,11 @@ __device__ __forceinline__ void encode_vector(const uint32_t (&row)[32], const u
     // acc collects code bits below the `have` bits it already holds; whole words leave from the top
     uint32_t wp = start >> 2, have = (start & 3u) * 8;   // the first word's leading bytes belong to the vector before
     unsigned long long acc = 0;
-    bool shared_word = true;                            // the next word to leave may be shared with a neighbour
     auto flush = [&]() {
         have -= 32u;
         const uint32_t word = (uint32_t)(acc >> have);
-        if (shared_word) { atomicOr(&out[wp], word); shared_word = false; }
-        else out[wp] = word;
-        wp++;
+        atomicOr(&out[wp], word);     // only a vector's first and last word can be shared with a neighbour, but one
+        wp++;                         // unconditional OR into the zeroed image issues fewer instructions than choosing
     };
 #pragma unroll
     for (int w = 0; w < 32; w++) {
