@@ -59,15 +59,36 @@ __device__ __forceinline__ uint32_t quant_one(__half x, const UnitParam &p, int 
     return (uint32_t)(int)c & 0xffu;
 }
 
-// quantise 8 halves held in a uint4 -> 8 code bytes in a uint2; optional smem histogram
+// quantise 8 halves held in a uint4 -> 8 code bytes in a uint2; optional smem histogram.
+// All eight go down the common path without a test in between (a unit with scale 0 has rcp = 0 and
+// min_int = 0 there, which yields code 0 by the same arithmetic); one test at the end sends the whole
+// chunk through quant_one again if any value fell outside 0..255 or was not finite.
 __device__ __forceinline__ uint2 quant_eight(const uint4 &v, const UnitParam *p, int pstride, int *flags,
                                              unsigned int *hist) {
     const __half *h = reinterpret_cast<const __half *>(&v);
     uint32_t c[8];
+    uint32_t odd = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        c[i] = quant_one(h[i], p[i * pstride], flags);
-        if (hist) atomicAdd(&hist[c[i]], 1u);
+        const UnitParam &u = p[i * pstride];
+        const float xf = __half2float(h[i]);
+        const float q0 = __fmul_rn(xf, u.rcp);
+        const float q1 = __fmaf_rn(__fmaf_rn(-q0, u.sf, xf), u.rcp, q0);
+        const float qh = __half2float(__float2half_rn(q1));
+        const float q = __fsub_rn(__fadd_rn(qh, KVC_RINT_MAGIC), KVC_RINT_MAGIC);
+        const float d = __fsub_rn(q, u.mi);
+        // d as an integer, read from the mantissa: in range exactly when 0 <= d <= 255
+        const uint32_t t = (uint32_t)__float_as_int(__fadd_rn(d, KVC_RINT_MAGIC)) - 0x4B400000u;
+        odd |= t;
+        c[i] = t & 0xffu;
+    }
+    if (odd > 255u) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) c[i] = quant_one(h[i], p[i * pstride], flags);
+    }
+    if (hist) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) atomicAdd(&hist[c[i]], 1u);
     }
     uint2 o;
     o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
