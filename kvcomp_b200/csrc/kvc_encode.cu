@@ -85,11 +85,17 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_sizes_kernel(
     uint16_t *__restrict__ thread_info, uint32_t *__restrict__ sizes, unsigned long long *__restrict__ partial,
     unsigned long long *__restrict__ max_block, int *__restrict__ status) {
     __shared__ __align__(16) uint8_t tile[64 * TILE_STRIDE];
-    __shared__ uint8_t lens[256];
+    // code lengths as 16-bit entries; a symbol without a code counts 1 << 14 instead, so that the sum of a
+    // vector (at most 128 * 32 bits) tells both its length and whether a symbol was missing, with no
+    // test per symbol
+    __shared__ uint16_t lens[256];
     __shared__ uint32_t wsum[2];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long blk = blockIdx.x;
-    for (int i = tid; i < 256; i += ENC_THREADS) lens[i] = i < n_entries ? (uint8_t)min(enc[2 * i + 1], 255u) : (uint8_t)0;
+    for (int i = tid; i < 256; i += ENC_THREADS) {
+        const uint32_t l = i < n_entries ? min(enc[2 * i + 1], 32u) : 0u;
+        lens[i] = (uint16_t)(l ? l : (1u << 14));
+    }
     stage_tile(tile, codes, blk, cols, is_k, tid);
     __syncthreads();
     int flags = 0;
@@ -99,12 +105,10 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_sizes_kernel(
     for (int w = 0; w < 32; w++) {
         const uint32_t x = rowp[w];
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const uint32_t l = lens[(x >> (8 * k)) & 0xffu];
-            if (l == 0) flags |= KVC_FLAG_SYMBOL_MISSING;
-            bits += l;
-        }
+        for (int k = 0; k < 4; k++) bits += lens[(x >> (8 * k)) & 0xffu];
     }
+    if (bits >> 14) flags |= KVC_FLAG_SYMBOL_MISSING;
+    bits &= (1u << 14) - 1;
     const uint32_t n = (bits + 7) >> 3;                      // the vector's bytes
     if (n > (is_k ? 128u : 256u)) flags |= KVC_FLAG_VECTOR_LONG;
     uint32_t wtotal;
