@@ -460,11 +460,22 @@ void orc_qk(const uint8_t *codes, const int16_t *min_int, const uint16_t *scale,
         }
 }
 
-/* kernels.cu:293-348 arithmetic exactly as the reference evaluates it: every
- * product and every running sum rounded to fp16, channel order.  Only used to
- * show how far the reference's own fp16 chain sits from the exact value. */
+/* The reference's own fp16 chain (kernels.cu:321): result = hadd(result, hmul(hmul(half(code + min_int),
+ * scale), B[c])), one channel after the other.  nvcc may contract the outer hmul with the hadd into one
+ * fp16 fma (a single rounding); `fused` selects that form, so a test can hold the reference's output to
+ * whichever the compiler chose.  The exact product of two fp16 values and its sum with a third fit a
+ * double, and _Float16 conversions from double are correctly rounded. */
+static inline uint16_t d2h(double d) { _Float16 v = (_Float16)d; uint16_t h; memcpy(&h, &v, 2); return h; }
+static inline uint16_t chain_step(uint16_t r, int value, uint16_t scale, uint16_t b, int fused) {
+    uint16_t v = f2h((float)value);
+    uint16_t p = f2h(h2f(v) * h2f(scale));
+    if (fused) return d2h((double)h2f(p) * (double)h2f(b) + (double)h2f(r));
+    p = f2h(h2f(p) * h2f(b));
+    return f2h(h2f(r) + h2f(p));
+}
+
 void orc_qk_fp16chain(const uint8_t *codes, const int16_t *min_int, const uint16_t *scale, const orc_qmeta *m,
-                      int64_t T, int64_t B, int64_t H, int64_t D, const uint16_t *q, uint16_t *S) {
+                      int64_t T, int64_t B, int64_t H, int64_t D, const uint16_t *q, uint16_t *S, int fused) {
     for (int64_t b = 0; b < B; b++)
         for (int64_t h = 0; h < H; h++)
             for (int64_t t = 0; t < T; t++) {
@@ -473,13 +484,28 @@ void orc_qk_fp16chain(const uint8_t *codes, const int16_t *min_int, const uint16
                 uint16_t r = f2h(0.0f);
                 for (int64_t c = 0; c < D; c++) {
                     int64_t u = ub + c * m->sc;
-                    uint16_t v = f2h((float)((int)codes[base + c] + (int)min_int[u]));
-                    uint16_t p = f2h(h2f(v) * h2f(scale[u]));
-                    p = f2h(h2f(p) * h2f(q[(b * H + h) * D + c]));
-                    r = f2h(h2f(r) + h2f(p));
+                    r = chain_step(r, (int)codes[base + c] + (int)min_int[u], scale[u], q[(b * H + h) * D + c], fused);
                 }
                 S[(b * H + h) * T + t] = r;
             }
+}
+
+/* The fused V kernel's partial outputs (kernels.cu:350-407, 778-861): for every group g of 128 tokens,
+ * C[g, b, h, c] = the fp16 chain over the group's tokens of half(code + min_int[t]) * scale[t] * P[b, h, t]. */
+void orc_pv_fp16chain(const uint8_t *codes, const int16_t *min_int, const uint16_t *scale, const orc_qmeta *m,
+                      int64_t T, int64_t B, int64_t H, int64_t D, const uint16_t *P, uint16_t *C, int fused) {
+    for (int64_t g = 0; g < T / 128; g++)
+        for (int64_t b = 0; b < B; b++)
+            for (int64_t h = 0; h < H; h++)
+                for (int64_t c = 0; c < D; c++) {
+                    uint16_t r = f2h(0.0f);
+                    for (int64_t t = g * 128; t < (g + 1) * 128; t++) {
+                        int64_t u = (t / m->tok_div) * m->sj + b * m->sb + h * m->sh + c * m->sc;
+                        r = chain_step(r, (int)codes[((t * B + b) * H + h) * D + c] + (int)min_int[u], scale[u],
+                                       P[(b * H + h) * T + t], fused);
+                    }
+                    C[((g * B + b) * H + h) * D + c] = r;
+                }
 }
 
 /* kernels.cu:778-861 + :350-407 (fused V) followed by the sum over token groups

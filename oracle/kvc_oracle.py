@@ -182,13 +182,24 @@ def qk(codes, mi, sc, m, q):
     return S
 
 
-def qk_fp16chain(codes, mi, sc, m, q):
+def qk_fp16chain(codes, mi, sc, m, q, fused=False):
+    """The reference's fp16 accumulation chain of the fused K kernel; fused: mul + add as one fp16 fma."""
     T, B, H, D = codes.shape
     q = np.ascontiguousarray(q, dtype=np.float16)
     S = np.empty((B, H, T), np.float16)
     lib().orc_qk_fp16chain(_p(codes), _p(_mi16(mi)), _p(sc), C.byref(m), _i64(T), _i64(B), _i64(H), _i64(D),
-                           _p(q), _p(S))
+                           _p(q), _p(S), C.c_int(int(fused)))
     return S
+
+
+def pv_fp16chain(codes, mi, sc, m, P, fused=False):
+    """The fused V kernel's per-group fp16 partials [T/128, B, H, D] for P fp16 [B, H, T]."""
+    T, B, H, D = codes.shape
+    P = np.ascontiguousarray(P, dtype=np.float16)
+    out = np.empty((T // 128, B, H, D), np.float16)
+    lib().orc_pv_fp16chain(_p(codes), _p(_mi16(mi)), _p(sc), C.byref(m), _i64(T), _i64(B), _i64(H), _i64(D),
+                           _p(P), _p(out), C.c_int(int(fused)))
+    return out
 
 
 def pv(codes, mi, sc, m, P):
