@@ -196,7 +196,8 @@ int kvc_fused_pv(const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t 
 /* One decode step of eager_attention_forward (models/llama.py:211-234) straight from the
  * compressed caches: out[b,hq,:] = softmax(q K^T * scaling) V over T compressed tokens
  * plus Tr uncompressed tail tokens (the recent window, ktail/vtail device fp16
- * [Tr,B,Hkv,128], may be NULL with Tr = 0).  q: device fp16 [B,Hq,128]; out: device fp16
+ * [Tr,B,Hkv,128], may be NULL with Tr = 0; with T = 0 only the tail is read and k, v may
+ * be NULL).  q: device fp16 [B,Hq,128]; out: device fp16
  * [B,Hq,128].  Scores never leave the SM; no fp16 K/V is written to memory.
  * Work is cut into items, one (sequence, KV head) column x one of `splits` equal runs of
  * 256-token tiles; as many CTAs as the device holds at once take items until none is left,
@@ -211,6 +212,13 @@ int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B
                     const void *q, float scaling, const void *ktail, const void *vtail, int64_t Tr,
                     void *out, int splits, void *workspace, int64_t workspace_bytes,
                     int32_t *status, kvc_stream_t stream);
+
+/* Diagnostics, no counterpart in the reference (its kernels have no device-side waits).  The attention
+ * kernel waits for its staged blocks at most `wait_limit` tries (0 = the default of 2^22); a wait that
+ * runs out raises KVC_FLAG_WAIT_TIMEOUT, the CTA stops taking work and the call returns.  starve != 0
+ * makes the kernel announce staging bytes that it never copies, so that a test can see a wait run out
+ * with nothing in flight; outputs of such a call are undefined.  Process-wide, read at every launch. */
+void kvc_attn_debug(int wait_limit, int starve);
 
 /* No counterpart in the reference.  kvc_attn_decode for callers that cannot allocate device memory
  * (a serving process whose memory pool owns the whole device, a plugin under a fixed memory budget):

@@ -72,6 +72,7 @@ _SIGNATURES = {
     "kvc_attn_splits": (_i32, [_i64, _i64, _i64, _i32]),
     "kvc_attn_decode": (_i32, [C.POINTER(Cache), C.POINTER(Cache), _i64, _i64, _i64, _i64, _vp, _f32, _vp, _vp,
                                _i64, _vp, _i32, _vp, _i64, _vp, _vp]),
+    "kvc_attn_debug": (None, [_i32, _i32]),
     "kvc_attn_static_capacity": (_i64, []),
     "kvc_attn_decode_static": (_i32, [C.POINTER(Cache), C.POINTER(Cache), _i64, _i64, _i64, _i64, _vp, _f32, _vp, _vp,
                                       _i64, _vp, _i32, _vp, _vp]),

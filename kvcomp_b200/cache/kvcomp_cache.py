@@ -6,11 +6,14 @@ models/llama.py:279-283,848-852, models/mistral.py:168-171,840-844, models/phi3.
     k, v = cache.update(key_states, value_states, layer_idx, {"cos": cos, "sin": sin})   # drop-in
     out = cache.attend(query_states, layer_idx, scaling)                                 # fused path
 
-`update` keeps the reference's contract: RoPE is applied to the new keys inside, the tokens are
-appended, and the whole cache comes back as fp16 [B, H, T, D] for eager attention -- compressed
-blocks dequantised (what the reference's simulated path returns, kvcomp_quant.py:70-75), recent
-tokens as they are.  `append` + `attend` is the path that never materialises K/V: the tokens go into
-the compressed store and one kernel computes softmax(q K^T * scaling) V straight from the streams.
+`update` keeps the reference's contract and returns the reference's values: RoPE is applied to the new
+keys inside, the tokens are appended, and the whole cache comes back as fp16 [B, H, T, D] for eager
+attention -- compressed blocks dequantised (what the reference's simulated path returns,
+kvcomp_quant.py:70-75), recent tokens as they are.  Like that path, quant units never span the batch
+(utils/compute.py:138-143) and min_ints are not narrowed to int8, unless the configuration's
+quant_per_sequence / wide_min_ints say otherwise.  `append` + `attend` is the path that never
+materialises K/V: the tokens go into the compressed store and one kernel computes
+softmax(q K^T * scaling) V straight from the streams.
 """
 import inspect
 import math
@@ -48,13 +51,17 @@ class KVCompCache(_BASE):
         self.coss = [None] * layer_num
         self.sins = [None] * layer_num
         self._ws = {}
+        self._status = {}
 
     # ---- appending --------------------------------------------------------------------------------
     def _ctx(self, layer_idx, kv_heads):
         cfg = KVCompCacheConfigStatic.config
         if self.k_ctx[layer_idx] is None:
-            self.k_ctx[layer_idx] = KVCompCtx(True, self.batch_size, kv_heads, self.head_dim, cfg.k_quant_scale_rel)
-            self.v_ctx[layer_idx] = KVCompCtx(False, self.batch_size, kv_heads, self.head_dim, cfg.v_quant_scale_rel)
+            kw = dict(batch_shared=getattr(cfg, "quant_per_sequence", None) is False,
+                      min_dtype=torch.int8 if getattr(cfg, "wide_min_ints", None) is False else torch.int16,
+                      keep_dequantised=True)
+            self.k_ctx[layer_idx] = KVCompCtx(True, self.batch_size, kv_heads, self.head_dim, cfg.k_quant_scale_rel, **kw)
+            self.v_ctx[layer_idx] = KVCompCtx(False, self.batch_size, kv_heads, self.head_dim, cfg.v_quant_scale_rel, **kw)
         return self.k_ctx[layer_idx], self.v_ctx[layer_idx]
 
     def append(self, key_states, value_states, layer_idx, cache_kwargs=None):
@@ -95,30 +102,28 @@ class KVCompCache(_BASE):
 
     # ---- fused decode attention -------------------------------------------------------------------
     def _tails(self, kc, vc):
-        """Compressed length the fused kernel reads and the fp16 tails that follow it.  K and V cut
-        their recent windows with different block and window sizes, so one of them may have a few more
-        compressed tokens than the other; those are dequantised into the tail."""
-        T = min(kc.compressed_ctx_len, vc.compressed_ctx_len) // 128 * 128
-        tails = []
-        for c in (kc, vc):
-            parts = []
-            if c.compressed_ctx_len > T:
-                x, _ = c.get_only_compressed()
-                parts.append(x[T:])
-            if c.buffer is not None and c.buffer.shape[0]:
-                parts.append(c.buffer)
-            tails.append(torch.cat(parts, dim=0).contiguous() if parts else None)
-        return T, tails[0], tails[1]
+        """Length of the range the fused kernel reads from the streams and the fp16 tails behind it.  K and V
+        cut their recent windows with different block and window sizes and fill Huffman blocks of
+        different length, so either may have quantised tokens beyond that range: their dequantised values
+        (kept since they were quantised) go in front of the recent window."""
+        T = min(kc.encoded_ctx_len, vc.encoded_ctx_len) // 128 * 128
+        return T, kc.tail_from(T), vc.tail_from(T)
+
+    def check(self):
+        """Raise if a fused launch since the last check reported a fatal condition (a stream that does not
+        decode, a staging wait that ran out).  Synchronises; attend() itself never does."""
+        for st in self._status.values():
+            flags = ops.read_status(st, what="attend")
+            if flags:
+                st.zero_()
 
     def attend(self, query_states, layer_idx, scaling=None):
         """One decode step: query_states [B, Hq, 1, D] (or [B, Hq, D]), already rotated -> attention
-        output of the same shape, computed straight from the compressed K and V of the layer."""
+        output of the same shape, computed straight from the compressed K and V of the layer; tokens
+        that are not in the streams yet (the recent window) are read as fp16 rows by the same kernel.
+        With pre-RoPE keys the stored keys are not rotated, every token would need its own rotation of
+        the query, and the step goes through the dequantised cache instead (the slow way)."""
         cfg = KVCompCacheConfigStatic.config
-        if not cfg.enable_quant or cfg.enable_pre_rope:
-            raise KvcError("attend needs enable_quant and post-RoPE keys; use update() otherwise")
-        kc, vc = self.k_ctx[layer_idx], self.v_ctx[layer_idx]
-        if kc is None:
-            raise KvcError("attend before any update")
         q = query_states
         squeeze = q.dim() == 4
         if squeeze:
@@ -128,15 +133,39 @@ class KVCompCache(_BASE):
         q = q.contiguous().half()
         B, Hq, D = q.shape
         scaling = 1.0 / math.sqrt(D) if scaling is None else scaling
+        if not cfg.enable_quant or cfg.enable_pre_rope:
+            out = self._attend_dense(q, layer_idx, scaling)
+            return out.unsqueeze(2) if squeeze else out
+        kc, vc = self.k_ctx[layer_idx], self.v_ctx[layer_idx]
+        if kc is None:
+            raise KvcError("attend before any update")
         T, ktail, vtail = self._tails(kc, vc)
         if T == 0 and ktail is None:
             raise KvcError("empty cache")
-        if T == 0:      # nothing compressed yet: the kernel only walks the fp16 rows, but still wants streams
-            raise KvcError("attend needs at least 128 compressed tokens; use update() while the cache is shorter")
         parts = ops.attn_splits(T, B, kc.head_num)          # partial results per head of the balanced split
         key = (q.device, B, Hq, parts)
         if key not in self._ws:
             self._ws[key] = ops.attn_workspace(B, Hq, parts, q.device)
-        out, st = ops.attn_decode(kc.cache(), vc.cache(), T, B, kc.head_num, q, scaling, ktail, vtail,
-                                  splits=0, workspace=self._ws[key])
+        if q.device not in self._status:
+            self._status[q.device] = ops.new_status(q.device)
+        out, _ = ops.attn_decode(kc.cache() if T else None, vc.cache() if T else None, T, B, kc.head_num, q, scaling,
+                                 ktail, vtail, splits=0, workspace=self._ws[key], status=self._status[q.device])
         return out.unsqueeze(2) if squeeze else out
+
+    def _attend_dense(self, q, layer_idx, scaling):
+        """softmax(q K^T * scaling) V over the materialised cache: plain fp16 caches (enable_quant off) and
+        pre-RoPE caches."""
+        cfg = KVCompCacheConfigStatic.config
+        if not cfg.enable_quant:
+            k, v = self.k_plain[layer_idx], self.v_plain[layer_idx]
+        else:
+            k = self.k_ctx[layer_idx].get()[0].permute(1, 2, 0, 3)
+            v = self.v_ctx[layer_idx].get()[0].permute(1, 2, 0, 3)
+        if k is None:
+            raise KvcError("attend before any update")
+        if cfg.enable_pre_rope:
+            k = apply_rotary_pos_emb_single(k, self.coss[layer_idx], self.sins[layer_idx])
+        g = q.shape[1] // k.shape[1]
+        kf, vf = k.float().repeat_interleave(g, dim=1), v.float().repeat_interleave(g, dim=1)
+        w = torch.softmax(torch.einsum("bhd,bhtd->bht", q.float(), kf) * scaling, dim=-1)
+        return torch.einsum("bht,bhtd->bhd", w, vf).half()

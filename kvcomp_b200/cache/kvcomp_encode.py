@@ -5,9 +5,12 @@ library: the quantiser is one kernel instead of ~8 torch ops, histogram and code
 device, and the stream grows inside pre-reserved arenas instead of torch.cat on every store
 (kvcomp_encode.py:129-133).  Beyond the reference: ChannelQuant / VectorQuant for K, per-sequence
 units, any batch size in the fused kernels, and `cache()` for the one-pass decode attention.
-"""
-from math import gcd
 
+Tokens are quantised in whole blocks of the configured block size, exactly where the reference cuts
+(utils/compute.py:44-72), and encoded in whole Huffman blocks (64 tokens for K, 128 for V).  When a V
+block size is not a multiple of 128 (the reference's CUDA path forbids that, kvcomp_encode.py:52-54; its
+model path allows it), up to 127 quantised tokens wait as plain codes for their vector to fill.
+"""
 import torch
 
 from .. import ops
@@ -41,7 +44,12 @@ class _Arena:
 
 class KVCompCtx:
     def __init__(self, is_k, batch_size, head_num, head_dim, quant_scale_rel,
-                 encode_codebook_path=None, decode_codebook_path=None):
+                 encode_codebook_path=None, decode_codebook_path=None, batch_shared=None, min_dtype=None,
+                 keep_dequantised=False):
+        """batch_shared / min_dtype: None takes the configuration's quant_per_sequence / wide_min_ints, and
+        where those are None too the reference's CUDA-path conventions (units span the batch, int8 min_ints).
+        keep_dequantised: keep the fp16 values of freshly quantised tokens until trim_dequantised() drops
+        them, so that a decode loop can hand the tokens behind the fused kernel's range over without decoding."""
         cfg = KVCompCacheConfigStatic.config
         assert cfg is not None, "KVCompCacheConfigStatic.config is None"
         assert head_dim == 128, "head_dim must be equal to K_VEC_LEN and V_VEC_LEN for cuda kernel implementation"
@@ -51,20 +59,32 @@ class KVCompCtx:
         self.quant_mode = cfg.k_quant_mode if is_k else cfg.v_quant_mode
         self.block_size = cfg.k_block_size if is_k else cfg.v_block_size
         self.recent_size = cfg.k_recent_size if is_k else cfg.v_recent_size
-        self.batch_shared = not getattr(cfg, "quant_per_sequence", False)
-        self.min_dtype = torch.int16 if getattr(cfg, "wide_min_ints", False) else torch.int8
+        if batch_shared is None:
+            per_seq = getattr(cfg, "quant_per_sequence", None)
+            batch_shared = True if per_seq is None else not per_seq
+        if min_dtype is None:
+            wide = getattr(cfg, "wide_min_ints", None)
+            min_dtype = torch.int16 if wide else torch.int8
+        self.batch_shared, self.min_dtype = bool(batch_shared), min_dtype
+        self.cut_block = self.block_size                     # tokens are quantised where the reference cuts
         if is_k:
             assert self.block_size % 64 == 0, "for K, block size must be divisible by VEC_PER_BLK"
             assert self.quant_mode in _MODE
-            self.cut_block = self.block_size
+            self.enc_block = 64
         else:
             assert self.quant_mode in (QuantMode.TokenQuant, QuantMode.VectorQuant, QuantMode.BlockQuant), \
                 "V units must not depend on the channel"
-            self.cut_block = self.block_size * 128 // gcd(self.block_size, 128)     # whole 128-token vectors
+            self.enc_block = 128                             # whole 128-token vectors
+        if self.quant_mode in (QuantMode.BlockQuant, QuantMode.ChannelQuant) and not is_k:
+            assert self.block_size % 128 == 0 or 128 % self.block_size == 0
         self.spec = ops.qspec(_MODE[self.quant_mode], self.batch_shared, batch_size, head_num, head_dim,
                               self.block_size)
         self.ctx_len = 0
-        self.compressed_ctx_len = 0
+        self.compressed_ctx_len = 0              # quantised tokens
+        self.encoded_ctx_len = 0                 # of those, the tokens in the stream (whole Huffman blocks)
+        self._pending = None                     # codes of quantised tokens whose Huffman block is not full yet
+        self.keep_dequantised = keep_dequantised
+        self._xhat, self._xhat_start = None, 0   # fp16 values of the quantised tokens from _xhat_start on
         self.device = None
         self.buffer = None                       # uncompressed recent tokens, fp16 [r, B, H, D]
         self.book = None
@@ -162,16 +182,34 @@ class KVCompCtx:
         codes, n_units, st_q = self._quantize(x, hist)
         if self.book is None:
             self.book = ops.build_codebook(hist)
-        ops.read_status(st_q, what="quantize")
-        if not self._encode(codes):
-            # A symbol the frozen book has no code for.  The reference drops such symbols silently
-            # (kernels.cu:197-205: a table entry of length 0 adds no bits), which corrupts the stream.
-            # Here the book is rebuilt over everything stored so far plus every reachable code, and the
-            # cache is re-encoded once; this cannot happen again for this context.
-            self._rebook(codes)
+        flags = ops.read_status(st_q, what="quantize")
+        if flags & ops._lib.FLAG_MIN_OVERFLOW:
+            # int8 is the reference's CUDA path, which wraps silently (kvcomp_encode.py:97); its model path
+            # keeps min_ints in floating point (utils/compute.py:89).  Wrapped values dequantise wrongly.
+            if self.min_dtype == torch.int16:
+                raise KvcError("a min_int does not fit 16 bits: the data lies too far from zero for its range")
+            import warnings
+            warnings.warn("a min_int wrapped in int8 as in the reference's CUDA path; set wide_min_ints to keep it")
+        if self.keep_dequantised:
+            mi = self._mi.buf[self._mi.n:self._mi.n + n_units]
+            sc = self._sc.buf[self._sc.n:self._sc.n + n_units]
+            xh = ops.dequant(codes, mi, sc, self.spec)
+            self._xhat = xh if self._xhat is None else torch.cat([self._xhat, xh], dim=0)
         self._mi.n += n_units
         self._sc.n += n_units
         self.compressed_ctx_len += T
+        pend = codes if self._pending is None else torch.cat([self._pending, codes], dim=0)
+        n_enc = pend.shape[0] // self.enc_block * self.enc_block
+        if n_enc:
+            part = pend[:n_enc].contiguous()
+            if not self._encode(part):
+                # A symbol the frozen book has no code for.  The reference drops such symbols silently
+                # (kernels.cu:197-205: a table entry of length 0 adds no bits), which corrupts the stream.
+                # Here the book is rebuilt over everything stored so far plus every reachable code, and the
+                # cache is re-encoded once; this cannot happen again for this context.
+                self._rebook(part)
+            self.encoded_ctx_len += n_enc
+        self._pending = pend[n_enc:].contiguous() if pend.shape[0] > n_enc else None
         return codes.view(-1, self.block_size, self.batch_size, self.head_num, self.head_dim)
 
     def _encode(self, codes):
@@ -198,9 +236,9 @@ class KVCompCtx:
 
     def _rebook(self, new_codes):
         old = None
-        if self.compressed_ctx_len:
+        if self.encoded_ctx_len:
             old, st = ops.decode(self._enc.used(), self._bi.used(), self._ti.used(), self.book,
-                                 self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k,
+                                 self.encoded_ctx_len, self.batch_size, self.head_num, self.is_k,
                                  max_block=self.max_block_bytes)
             ops.read_status(st, what="entropy_decode")
         hist = ops.histogram(new_codes.view(-1))
@@ -247,12 +285,17 @@ class KVCompCtx:
         self._require()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        out, st = ops.decode(self._enc.used(), self._bi.used(), self._ti.used(), self.book,
-                             self.compressed_ctx_len, self.batch_size, self.head_num, self.is_k,
-                             max_block=self.max_block_bytes)
+        out = None
+        if self.encoded_ctx_len:
+            out, st = ops.decode(self._enc.used(), self._bi.used(), self._ti.used(), self.book,
+                                 self.encoded_ctx_len, self.batch_size, self.head_num, self.is_k,
+                                 max_block=self.max_block_bytes)
         stop.record()
         stop.synchronize()
-        ops.read_status(st, what="entropy_decode")
+        if out is not None:
+            ops.read_status(st, what="entropy_decode")
+        if self._pending is not None:
+            out = self._pending if out is None else torch.cat([out, self._pending], dim=0)
         return out.view(-1, self.block_size, self.batch_size, self.head_num, self.head_dim), start.elapsed_time(stop)
 
     def get_only_compressed(self):
@@ -274,8 +317,9 @@ class KVCompCtx:
         return (torch.cat([x, self.buffer], dim=0) if self.buffer is not None and self.buffer.shape[0] else x), t
 
     def cache(self):
-        """The kvc_cache argument of the fused kernels (valid until the next store)."""
-        self._require()
+        """The kvc_cache argument of the fused kernels over the encoded_ctx_len tokens of the stream (valid
+        until the next store)."""
+        assert self.encoded_ctx_len > 0 and self.book is not None, "nothing has been encoded yet"
         return ops.make_cache(self._enc.buf, self._bi.buf, self._ti.buf, self.book, self._mi.buf, self._sc.buf,
                               self.spec, self._enc.n, self.max_block_bytes)
 
@@ -283,6 +327,9 @@ class KVCompCtx:
         """K: scores [batch, heads, ctx] = q . K^T; V: [1, batch, heads, 128] = P . V over the compressed
         tokens (kvcomp_encode.py:209-280).  Returns (tensor, ms)."""
         self._require()
+        if self._pending is not None:
+            raise KvcError("mat_vec_mul: %d quantised tokens are not in the stream yet (V block sizes that are "
+                           "no multiple of 128 leave such a rest)" % self._pending.shape[0])
         assert B.dtype == torch.float16, "B must be float16"
         assert len(B.shape) == 3, "B must be 3D tensor"
         assert B.shape[0] == self.batch_size, "batch size mismatch"
@@ -317,5 +364,33 @@ class KVCompCtx:
         """Compression ratio with the reference's accounting (kvcomp_encode.py:317-326)."""
         compressed = (self._bi.n + self._ti.n * 2 + self._enc.n + self._mi.n * self._mi.used().element_size() +
                       self._sc.n * 2)
+        pending = 0 if self._pending is None else self._pending.numel()
         original = 2 * self.batch_size * self.compressed_ctx_len * self.head_num * self.head_dim
-        return original / compressed
+        return original / (compressed + pending)
+
+    # ---- the tokens behind the fused kernel's range ---------------------------------------------------
+    def tail_from(self, T):
+        """fp16 [n, B, H, D]: the quantised tokens from index T on (dequantised) followed by the recent
+        window.  Needs keep_dequantised; tokens before T are dropped from the kept values."""
+        parts = []
+        if self.compressed_ctx_len > T:
+            if not self.keep_dequantised or self._xhat is None or self._xhat_start > T:
+                x, _ = self.get_only_compressed()                 # decodes the whole stream: the slow way
+                parts.append(x[T:])
+            else:
+                self.trim_dequantised(T)
+                parts.append(self._xhat)
+        elif self.keep_dequantised:
+            self.trim_dequantised(T)
+        if self.buffer is not None and self.buffer.shape[0]:
+            parts.append(self.buffer)
+        if not parts:
+            return None
+        return parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+
+    def trim_dequantised(self, T):
+        T = min(T, self.compressed_ctx_len)
+        if self._xhat is not None and T > self._xhat_start:
+            self._xhat = self._xhat[T - self._xhat_start:] if T < self.compressed_ctx_len else None
+        if self._xhat is None or T > self._xhat_start:
+            self._xhat_start = T

@@ -181,10 +181,12 @@ __device__ __forceinline__ bool book_has_long_codes(const void *book) {
 
 // ---- staging --------------------------------------------------------------------------------------
 // plain loads: the 64 threads of a sub-group copy block `blk` into `slot`
-__device__ __forceinline__ bool stage(const CacheDev &kc, long long blk, uint8_t *slot, uint32_t *lead, int v) {
+// *nb receives the block's byte count: a vector that starts at or beyond it is not decoded
+__device__ __forceinline__ bool stage(const CacheDev &kc, long long blk, uint8_t *slot, uint32_t *lead, uint32_t *nb, int v) {
     const uint2 bi = kc.block_info[blk];
     const uint32_t nbytes = bi.y & 0xffffu;
-    if (nbytes == 0 || nbytes > kc.max_block || (long long)bi.x + nbytes > kc.encoded_bytes) { *lead = 0; return false; }
+    *nb = nbytes;
+    if (nbytes == 0 || nbytes > kc.max_block || (long long)bi.x + nbytes > kc.encoded_bytes) { *lead = 0; *nb = 0; return false; }
     *lead = kvc_stage_block(slot, kc.encoded, kc.encoded_bytes, bi.x, nbytes, v, 64);
     return true;
 }
@@ -192,14 +194,16 @@ __device__ __forceinline__ bool stage(const CacheDev &kc, long long blk, uint8_t
 // bulk copies: lane `l` (< 4) of one warp issues the copy of its block; the whole warp must call.
 // The source range is widened to 16-byte boundaries; `encoded` is 16-byte aligned and readable to
 // the next boundary past its end (checked / required by the host code).
+// starve (tests of the bounded waits only): announce 16 bytes and copy nothing, so that the phase never
+// completes and nothing is in flight when the waiting threads give up.
 __device__ __forceinline__ void stage_bulk(const CacheDev &kc, bool valid, long long blk, uint8_t *slot,
-                                           uint32_t *lead, int *ok, uint64_t *bar, int lane) {
-    uint32_t bytes = 0, ld = 0;
+                                           uint32_t *lead, int *ok, uint32_t *nb, uint64_t *bar, int lane, bool starve = false) {
+    uint32_t bytes = 0, ld = 0, nbytes = 0;
     const uint8_t *a0 = nullptr;
     bool good = false;
     if (lane < 4 && valid) {
         const uint2 bi = kc.block_info[blk];
-        const uint32_t nbytes = bi.y & 0xffffu;
+        nbytes = bi.y & 0xffffu;
         good = nbytes != 0 && nbytes <= kc.max_block && (long long)bi.x + nbytes <= kc.encoded_bytes;
         if (good) {
             const uint8_t *src = kc.encoded + bi.x;
@@ -208,13 +212,14 @@ __device__ __forceinline__ void stage_bulk(const CacheDev &kc, bool valid, long 
             bytes = (ld + nbytes + 15u) & ~15u;
         }
     }
+    if (starve) bytes = 0;
     uint32_t total = bytes;
     total += __shfl_xor_sync(0xffffffffu, total, 1);
     total += __shfl_xor_sync(0xffffffffu, total, 2);
-    if (lane == 0) kvc_mbar_expect_tx(bar, total);            // one arrival per phase, even for 0 bytes
+    if (lane == 0) kvc_mbar_expect_tx(bar, starve ? 16u : total);   // one arrival per phase, even for 0 bytes
     __syncwarp();
     if (lane < 4) {
-        lead[lane] = ld; ok[lane] = good;
+        lead[lane] = ld; ok[lane] = good; nb[lane] = good ? nbytes : 0u;
         if (bytes) kvc_bulk_g2s(slot, a0, bytes, bar);
     }
 }
@@ -419,7 +424,7 @@ struct QkSmem {
     float zp[4 * G];
     float qf[G * 128];
     float qsum[G];
-    uint32_t lead[4];
+    uint32_t lead[4], nb[4];
     int ok[4];
 };
 
@@ -438,7 +443,7 @@ __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T
     load_q<G>(sm.qf, sm.qsum, q, b, Hq, hq0, 1.0f, tid);
     const long long blk = (tok0 / 64 + sub) * cols + col;
     const bool active = t < T;
-    if (active) { uint32_t ld; bool ok = stage(kc, blk, sm.slot[sub], &ld, v); if (v == 0) { sm.lead[sub] = ld; sm.ok[sub] = ok; } }
+    if (active) { uint32_t ld, nb; bool ok = stage(kc, blk, sm.slot[sub], &ld, &nb, v); if (v == 0) { sm.lead[sub] = ld; sm.nb[sub] = nb; sm.ok[sub] = ok; } }
     __syncthreads();
     k_weights<G>(sm.w, sm.step, sm.zp, sm.qf, kc.q, tok0, T, b, h, tid);
     __syncthreads();
@@ -448,8 +453,9 @@ __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T
     int hi[G], lo[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
-    bool ok = sm.ok[sub];
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(kc.thread_info, blk, v), sm.book, esc, sm.w + sub * 2 * WROW * G, hi, lo);
+    const uint32_t start = vec_start(kc.thread_info, blk, v);
+    bool ok = sm.ok[sub] && start < sm.nb[sub];                // a vector begins inside its block
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + start, sm.book, esc, sm.w + sub * 2 * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
     float s[G];
     k_finish<G>(s, hi, lo, sm.step + sub * G, sm.zp + sub * G, sm.qsum, kc.q.sc != 0, kvc_scale_value(ksc), (float)kmi);
@@ -471,7 +477,7 @@ struct PvSmem {
     float zpv[2 * G];
     float red[2][8 * G];
     int16_t q16[2 * G * 132];
-    uint32_t lead[4];
+    uint32_t lead[4], nb[4];
     int ok[4];
 };
 
@@ -492,7 +498,7 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
     const long long gI = tok0 / 128 + grp;
     const long long blk = gI * (cols * 2) + col * 2 + (ch >> 6);
     const bool active = gI * 128 < T;
-    if (active) { uint32_t ld; bool ok = stage(vc, blk, sm.slot[sub], &ld, v); if (v == 0) { sm.lead[sub] = ld; sm.ok[sub] = ok; } }
+    if (active) { uint32_t ld, nb; bool ok = stage(vc, blk, sm.slot[sub], &ld, &nb, v); if (v == 0) { sm.lead[sub] = ld; sm.nb[sub] = nb; sm.ok[sub] = ok; } }
     float wv[G];
     {
         float sc = 0.f, mi = 0.f;
@@ -513,8 +519,9 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
     int hi[G], lo[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
-    bool ok = sm.ok[sub];
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + vec_start(vc.thread_info, blk, v), sm.book, esc, sm.ps + grp * 2 * WROW * G, hi, lo);
+    const uint32_t start = vec_start(vc.thread_info, blk, v);
+    bool ok = sm.ok[sub] && start < sm.nb[sub];
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + start, sm.book, esc, sm.ps + grp * 2 * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
 #pragma unroll
     for (int g = 0; g < G; g++) {
@@ -537,8 +544,10 @@ struct alignas(32) AttnSmem {                     // followed in shared memory b
     float red[4][8 * G];              // per-warp max, sum, zpv and weight-max partials
     uint64_t bar[2];                  // K and V staging barriers
     uint32_t leadK[4], leadV[4];
+    uint32_t nbK[4], nbV[4];          // byte counts of the staged blocks
     int okK[4], okV[4];
     int next_j;                       // item the CTA drew for after the current one
+    int dead;                         // a staging wait ran out: the CTA takes no further tiles
 };
 
 struct AttnParams {
@@ -556,6 +565,8 @@ struct AttnParams {
     float *ws_part;               // [B*Hq][splits][ATTN_PART_FLOATS]
     int *sched;                   // {items handed out, CTAs finished}, or null: static shares
     int *status;
+    int wait_limit;               // tries of a staging wait before it gives up (KVC_FLAG_WAIT_TIMEOUT)
+    int starve;                   // tests of the bounded waits only: announce bytes that are never copied
 };
 
 // BULK: stage with bulk asynchronous copies (one tile phase ahead) instead of plain loads.
@@ -575,7 +586,9 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     const long long cols = B * Hkv, Gt = Hq / Hkv;
     const int n_tiles = p.n_tiles;
     const kvc_qmeta_dev &km = p.k.q, &vm = p.v.q;
+    const bool starve = BULK && p.starve != 0;
     int flags = 0;
+    bool dead = false;                                     // a staging wait ran out (uniform over the CTA after the next barrier)
 
     // The work is cut into items: a column (one sequence, one KV head) x one of `splits` runs of
     // `tiles_per_split` tiles; item j = column * splits + run.  Without a scheduling counter CTA i of P
@@ -613,16 +626,19 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     const bool any_tiles = have && it.t_lo < it.t_hi;      // items are empty only when the cache has no compressed part
 
     if (BULK) {
-        if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); }
+        if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); sm.dead = 0; }
         __syncthreads();
         if (warp == 0 && any_tiles) {
-            stage_bulk(p.k, validK(true, it.t_lo, lane & 3), blkK_of(it.col, it.t_lo, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
-            stage_bulk(p.v, validV(true, it.t_lo, lane & 3), blkV_of(it.col, it.t_lo, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
+            stage_bulk(p.k, validK(true, it.t_lo, lane & 3), blkK_of(it.col, it.t_lo, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, sm.nbK, &sm.bar[0], lane, starve);
+            stage_bulk(p.v, validV(true, it.t_lo, lane & 3), blkV_of(it.col, it.t_lo, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, sm.nbV, &sm.bar[1], lane, starve);
         }
+    } else if (tid == 0) sm.dead = 0;
+    bool escK = false, escV = false;
+    if (p.T > 0) {                                         // (no streams at all while nothing is compressed yet)
+        kvc_load_book(sm.bookK, p.k.book, tid, NTHR);
+        kvc_load_book(sm.bookV, p.v.book, tid, NTHR);
+        escK = book_has_long_codes(p.k.book); escV = book_has_long_codes(p.v.book);
     }
-    kvc_load_book(sm.bookK, p.k.book, tid, NTHR);
-    kvc_load_book(sm.bookV, p.v.book, tid, NTHR);
-    const bool escK = book_has_long_codes(p.k.book), escV = book_has_long_codes(p.v.book);
 
     // Per-thread metadata of a tile (vector start offsets, the token's V scale / min_int, the K unit
     // parameters of the warp's block) is fetched one tile ahead, so that no global-memory latency
@@ -668,7 +684,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     };
     if (have) q_fetch(it.col);
 
-    uint32_t phase = 0;
+    uint32_t parK = 0, parV = 0;                           // parity of the staging phase each barrier is waited for next
     while (have) {
     const int col = it.col, b = col / (int)Hkv, h = col % (int)Hkv;
     const long long hq0 = h * Gt + p.g0;
@@ -681,7 +697,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 #pragma unroll
     for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
 
-    for (int tile = it.t_lo; tile < it.t_hi; tile++, phase ^= 1u) {
+    for (int tile = it.t_lo; tile < it.t_hi; tile++) {
         const long long tok0 = (long long)tile * 256, t = tok0 + tid;
         const long long blkK = (tok0 / 64 + sub) * cols + col;
         const long long gI = tok0 / 128 + grp;
@@ -695,19 +711,26 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         }
         load_meta(n_on, n_col, n_tile, nxt);
         if (!BULK) {
-            if (actK) { uint32_t ld; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, v); if (v == 0) { sm.leadK[sub] = ld; sm.okK[sub] = ok; } }
-            if (actV) { uint32_t ld; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, v); if (v == 0) { sm.leadV[sub] = ld; sm.okV[sub] = ok; } }
+            if (actK) { uint32_t ld, nb; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, &nb, v); if (v == 0) { sm.leadK[sub] = ld; sm.nbK[sub] = nb; sm.okK[sub] = ok; } }
+            if (actV) { uint32_t ld, nb; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, &nb, v); if (v == 0) { sm.leadV[sub] = ld; sm.nbV[sub] = nb; sm.okV[sub] = ok; } }
         }
         k_weights_build<G, ROWS>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, tok0, T, tid);
-        if (BULK && !kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
+        // A wait that runs out: the tile is not decoded, the CTA issues no further copies and takes no
+        // further tiles (what it had in flight is waited for once more, bounded, before it returns).
+        if (BULK) {
+            if (kvc_mbar_wait(&sm.bar[0], parK, p.wait_limit)) parK ^= 1u;
+            else { flags |= KVC_FLAG_WAIT_TIMEOUT; sm.dead = 1; }
+        }
         __syncthreads();
+        dead = BULK && sm.dead != 0;
+        if (dead) break;
         // ---- K: scores of this tile's tokens
         float s[G];
         if (actK) {
             int hi[G], lo[G];
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
-            bool ok = sm.okK[sub];
+            bool ok = sm.okK[sub] && (uint32_t)(cur.startK >> 3) < sm.nbK[sub];      // a vector begins inside its block
             if (ok) {
                 if constexpr (ROWS) ok = decode_rows<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, myrow, sm.w + sub * VecWords<G, true>::value, hi, lo);
                 else ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, sm.w + sub * VecWords<G, false>::value, hi, lo);
@@ -723,7 +746,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         for (int g = 0; g < G; g++) { float mx = kvc_warp_max(s[g]); if (lane == 0) sm.red[0][warp * G + g] = mx; }
         __syncthreads();                                   // also: every thread is done with the K slots
         if (BULK && warp == 0)                             // next tile's K blocks land during the V phase
-            stage_bulk(p.k, validK(n_on, n_tile, lane & 3), blkK_of(n_col, n_tile, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, &sm.bar[0], lane);
+            stage_bulk(p.k, validK(n_on, n_tile, lane & 3), blkK_of(n_col, n_tile, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, sm.nbK, &sm.bar[0], lane, starve);
         float alpha[G], wv[G];
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -747,7 +770,9 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             for (int w8 = 0; w8 < 8; w8++) lt += sm.red[1][w8 * G + g];
             l_run[g] = l_run[g] * alpha[g] + lt;
         }
-        if (BULK && !kvc_mbar_wait(&sm.bar[1], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
+        const bool v_landed = !BULK || kvc_mbar_wait(&sm.bar[1], parV, p.wait_limit);
+        if (BULK && v_landed) parV ^= 1u;
+        if (!v_landed) { flags |= KVC_FLAG_WAIT_TIMEOUT; sm.dead = 1; }     // seen by all at the tile's last barrier
         // ---- V: accumulate this tile's contribution for the thread's (group, channel)
         float dv[G];
 #pragma unroll
@@ -756,7 +781,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             int hi[G], lo[G];
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
-            bool ok = sm.okV[sub];
+            bool ok = v_landed && sm.okV[sub] && (uint32_t)(cur.startV >> 3) < sm.nbV[sub];
             if (ok) {
                 if constexpr (ROWS) ok = decode_rows<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, myrow, sm.ps + grp * VecWords<G, true>::value, hi, lo);
                 else ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, sm.ps + grp * VecWords<G, false>::value, hi, lo);
@@ -771,10 +796,13 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 #pragma unroll
         for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
         __syncthreads();                                   // every thread is done with the V slots, weights and sums
+        dead = BULK && sm.dead != 0;
+        if (dead) break;                                   // (the K copy issued above is waited for at the end)
         if (BULK && warp == 0)                             // next tile's V blocks land during its K phase
-            stage_bulk(p.v, validV(n_on, n_tile, lane & 3), blkV_of(n_col, n_tile, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, &sm.bar[1], lane);
+            stage_bulk(p.v, validV(n_on, n_tile, lane & 3), blkV_of(n_col, n_tile, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, sm.nbV, &sm.bar[1], lane, starve);
         cur = nxt;
     }
+    if (dead) break;                                       // no partial result is written: the status word says why
 
     // ---- uncompressed tail (the recent window), handled with the column's last tiles: dense fp16 rows
     if (p.Tr > 0 && it.t_hi == n_tiles) {
@@ -867,9 +895,10 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     it = nit; have = have_next; j_it = j_n1; j_n1 = j_n2;
     have_next = have && item_of(j_n1, nit);
     }   // items of the CTA
-    if (BULK && any_tiles) {              // the copies issued after the last tile are empty, but their phase must end
-        if (!kvc_mbar_wait(&sm.bar[0], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
-        if (!kvc_mbar_wait(&sm.bar[1], phase)) flags |= KVC_FLAG_WAIT_TIMEOUT;
+    if (BULK && any_tiles) {              // the copies issued after the last tile are empty, but their phase must end;
+        // after a wait that ran out, these are the phases still open: nothing may be in flight at the return
+        if (!kvc_mbar_wait(&sm.bar[0], parK, p.wait_limit)) flags |= KVC_FLAG_WAIT_TIMEOUT;
+        if (!kvc_mbar_wait(&sm.bar[1], parV, p.wait_limit)) flags |= KVC_FLAG_WAIT_TIMEOUT;
     }
     if (flags) atomicOr(p.status, flags);
     if (draw && tid == 0) {               // the last CTA to finish leaves the scheduling counters zeroed for the next launch
@@ -991,6 +1020,10 @@ extern "C" int kvc_fused_pv(const kvc_cache *v, int64_t T, int64_t B, int64_t Hk
     return KVC_OK;
 }
 
+// Diagnostics for tests of the bounded waits (kvc_attn_debug): process-wide, read at every launch.
+static int g_wait_limit = 0, g_starve = 0;
+extern "C" void kvc_attn_debug(int wait_limit, int starve) { g_wait_limit = wait_limit; g_starve = starve; }
+
 // CTAs per SM the attention kernel is launched with at most (its launch bounds ask for this many)
 constexpr int ATTN_CTAS_PER_SM = 3;
 // items a resident CTA should get on average: enough that the draws even out the CTAs' speeds and the
@@ -1042,8 +1075,10 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
                                const void *q, float scaling, const void *ktail, const void *vtail, int64_t Tr,
                                void *out, int splits, void *workspace, int64_t workspace_bytes,
                                int32_t *status, kvc_stream_t stream) {
-    if (int rc = check_cache(k, "kvc_attn_decode", true)) return rc;
-    if (int rc = check_cache(v, "kvc_attn_decode", false)) return rc;
+    if (T > 0) {      // with nothing compressed yet only the fp16 tail is read and the caches may be NULL
+        if (int rc = check_cache(k, "kvc_attn_decode", true)) return rc;
+        if (int rc = check_cache(v, "kvc_attn_decode", false)) return rc;
+    }
     KVC_REQUIRE(q && out && status, "kvc_attn_decode: null pointer");
     KVC_REQUIRE(B > 0 && Hkv > 0 && Hq > 0 && Hq % Hkv == 0, "kvc_attn_decode: bad head counts");
     KVC_REQUIRE(T >= 0 && T % 128 == 0, "kvc_attn_decode: the compressed length must be a multiple of 128, got %lld", (long long)T);
@@ -1071,7 +1106,8 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
         KVC_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "kvc_attn_decode: workspace must be 16-byte aligned");
     }
     AttnParams p;
-    p.k = to_dev(*k); p.v = to_dev(*v);
+    if (T > 0) { p.k = to_dev(*k); p.v = to_dev(*v); }
+    else { p.k = CacheDev(); p.v = CacheDev(); p.k.q.tok_div = p.v.q.tok_div = 1; }
     p.T = T; p.B = B; p.Hkv = Hkv; p.Hq = Hq; p.Tr = Tr;
     p.q = reinterpret_cast<const __half *>(q);
     p.ktail = reinterpret_cast<const __half *>(ktail); p.vtail = reinterpret_cast<const __half *>(vtail);
@@ -1084,13 +1120,15 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     p.sched = have_ws ? reinterpret_cast<int *>(workspace) : nullptr;
     p.ws_part = have_ws ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) + ATTN_COUNTER_BYTES) : nullptr;
     p.status = status;
+    p.wait_limit = g_wait_limit > 0 ? g_wait_limit : KVC_WAIT_LIMIT;
+    p.starve = g_starve;
     // a slot holds the largest block plus its alignment lead, widened to 16-byte chunks, plus the
     // decoder's two words of read-ahead
     p.slotK_bytes = ((p.k.max_block + 15u + 15u) & ~15u) + 16u;
     p.slotV_bytes = ((p.v.max_block + 15u + 15u) & ~15u) + 16u;
     const size_t slot_total = 4 * (size_t)(p.slotK_bytes + p.slotV_bytes) + SLOT_PAD;
     // bulk copies widen every block to 16-byte boundaries: both streams must start on one
-    const bool bulk = (reinterpret_cast<uintptr_t>(k->encoded) & 15) == 0 && (reinterpret_cast<uintptr_t>(v->encoded) & 15) == 0;
+    const bool bulk = T > 0 && (reinterpret_cast<uintptr_t>(k->encoded) & 15) == 0 && (reinterpret_cast<uintptr_t>(v->encoded) & 15) == 0;
     const int sms = kvc_sm_count();
     const long long Gt = Hq / Hkv;
     for (long long g0 = 0; g0 < Gt;) {
@@ -1157,7 +1195,9 @@ extern "C" int kvc_attn_decode_static(const kvc_cache *k, const kvc_cache *v, in
                                       const void *q, float scaling, const void *ktail, const void *vtail, int64_t Tr,
                                       void *out, int splits, int32_t *status, kvc_stream_t stream) {
     KVC_REQUIRE(B > 0 && Hkv > 0 && Hq > 0 && T >= 0, "kvc_attn_decode_static: bad shape");
-    const int parts = splits <= 0 ? kvc_attn_splits(T, B, Hkv, 0) : splits;      // partial results per head
+    // partial results per head: kvc_attn_decode never cuts a column into more runs than it has tiles
+    const long long n_tiles = (T + 255) / 256;
+    const int parts = splits <= 0 ? kvc_attn_splits(T, B, Hkv, 0) : (int)(splits > n_tiles ? (n_tiles > 0 ? n_tiles : 1) : splits);
     const int64_t need = kvc_attn_workspace(B, Hq, parts);
     if (need > KVC_STATIC_SCRATCH_BYTES) {
         kvc_set_error("kvc_attn_decode_static: B=%lld x Hq=%lld x %d splits needs %lld bytes of scratch, the built-in "

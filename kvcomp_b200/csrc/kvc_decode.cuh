@@ -66,10 +66,12 @@ __device__ __forceinline__ void kvc_bulk_g2s(void *dst, const void *src, uint32_
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(kvc_smem_addr(dst)), "l"(src), "r"(bytes), "r"(kvc_smem_addr(bar)) : "memory");
 }
-// Bounded wait for the phase with the given parity.  Returns false if it never completed.
-__device__ __forceinline__ bool kvc_mbar_wait(uint64_t *bar, uint32_t parity) {
+// Bounded wait for the phase with the given parity: at most `limit` tries.  Returns false if the phase
+// never completed.
+#define KVC_WAIT_LIMIT (1 << 22)
+__device__ __forceinline__ bool kvc_mbar_wait(uint64_t *bar, uint32_t parity, int limit = KVC_WAIT_LIMIT) {
     const uint32_t a = kvc_smem_addr(bar);
-    for (int it = 0; it < (1 << 22); it++) {
+    for (int it = 0; it < limit; it++) {
         uint32_t done;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(done) : "r"(a), "r"(parity) : "memory");

@@ -301,11 +301,18 @@ def attn_decode(kcache, vcache, T, B, Hkv, q, scaling, ktail=None, vtail=None, o
     elif workspace is False:        # no workspace at all (splits must be 1): the CTAs take fixed shares of the columns
         workspace = torch.empty(0, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
-        _lib.check(lib.kvc_attn_decode(C.byref(kcache), C.byref(vcache), T, B, Hkv, Hq, _p(q), float(scaling),
+        _lib.check(lib.kvc_attn_decode(C.byref(kcache) if kcache is not None else None,
+                                       C.byref(vcache) if vcache is not None else None, T, B, Hkv, Hq, _p(q), float(scaling),
                                        _p(ktail), _p(vtail), Tr, _p(out), int(splits),
                                        _p(workspace if workspace.numel() else None), workspace.numel(),
                                        _p(status), _stream()), "kvc_attn_decode")
     return out, status
+
+
+def attn_debug(wait_limit=0, starve=False):
+    """Diagnostics of the attention kernel's bounded staging waits (kvc_attn_debug); (0, False) restores
+    the defaults."""
+    _lib.load().kvc_attn_debug(int(wait_limit), int(bool(starve)))
 
 
 def attn_decode_static(kcache, vcache, T, B, Hkv, q, scaling, out, ktail=None, vtail=None, splits=0, status=None):
@@ -319,6 +326,8 @@ def attn_decode_static(kcache, vcache, T, B, Hkv, q, scaling, out, ktail=None, v
         raise KvcError("attn_decode_static: pass a status tensor (ops.new_status) made beforehand")
     Tr = 0
     if ktail is not None and ktail.shape[0] > 0:
+        _cuda(ktail, torch.float16, "ktail")
+        _cuda(vtail, torch.float16, "vtail")
         Tr = ktail.shape[0]
     else:
         ktail = vtail = None

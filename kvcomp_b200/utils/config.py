@@ -1,6 +1,8 @@
 """The reference's configuration object (utils/config.py:21-140) and its global holder
 (models/cache/kvcomp_quant.py:10-12), with the same fields, str()/from_str() round trip, equality and
-hash.  Two optional fields are added (both default to the reference's behaviour)."""
+hash.  Two optional fields are added; left at None, each cache class follows the reference class it
+replaces (KVCompCtx: the CUDA path's batch-spanning units and int8 min_ints; KVCompCache: the model
+path's per-sequence units and un-narrowed min_ints)."""
 from .compute import QuantMode
 
 
@@ -24,7 +26,7 @@ class KVCompCacheConfig:
 
     def __init__(self, model_name, k_quant_mode, v_quant_mode, k_block_size, v_block_size, k_recent_size,
                  v_recent_size, k_quant_scale_rel, v_quant_scale_rel, enable_quant=True, enable_pre_rope=False,
-                 quant_per_sequence=False, wide_min_ints=False):
+                 quant_per_sequence=None, wide_min_ints=None):
         self.enable_quant = enable_quant
         self.model_name = model_name
         self.enable_pre_rope = enable_pre_rope
@@ -36,8 +38,9 @@ class KVCompCacheConfig:
         self.v_recent_size = v_recent_size
         self.k_quant_scale_rel = k_quant_scale_rel
         self.v_quant_scale_rel = v_quant_scale_rel
-        # additions: quant units per sequence instead of spanning the batch (the reference's CUDA path
-        # spans it, models/cache/kvcomp_encode.py:10-13); int16 instead of int8 min_ints
+        # additions (None = the default of the cache class in use): quant units per sequence
+        # (utils/compute.py:138-143) or spanning the batch (models/cache/kvcomp_encode.py:10-13);
+        # int16 or int8 (kvcomp_encode.py:97) min_ints
         self.quant_per_sequence = quant_per_sequence
         self.wide_min_ints = wide_min_ints
 

@@ -17,6 +17,9 @@ Fixtures written:
                       utils/huffman.py:huffman_encode, its total bit count, and the
                       (shift, encode bytes, decode bytes) of src/huffman.cpp:build_codebook
   flat_golden.npz     a small code tensor and the flat bitstream utils/huffman.py makes of it
+  update_golden.npz   what the model-facing cache returns (models/cache/kvcomp_quant.py:29-75: RoPE on the
+                      new keys, utils/compute.py:quant_error for K and V) over a prefill followed by
+                      single-token updates, batch 2, for five mode / block / pre-RoPE settings
 """
 import json
 import os
@@ -31,7 +34,8 @@ REF = os.environ.get("REF", "/root/reference")
 sys.path.insert(0, REPO)
 sys.path.insert(0, REF)
 
-from utils.compute import quant, quant_ints, QuantMode, cut_tensor_ctx_len_0, cut_tensor  # noqa: E402
+from utils.compute import (quant, quant_ints, QuantMode, cut_tensor_ctx_len_0, cut_tensor, quant_error,  # noqa: E402
+                           apply_rotary_pos_emb_single, safe_cat)
 from utils.huffman import huffman_encode  # noqa: E402
 from oracle import build_ref  # noqa: E402
 
@@ -171,7 +175,76 @@ def make_flat():
     print("flat_golden.npz:", bits.numel(), "bits")
 
 
+UPDATE_CASES = (
+    # name, K mode, K block, K recent, K rel, V mode, V block, V recent, V rel, pre-RoPE
+    ("channel_token", "ChannelQuant", 64, 64, 0.05, "TokenQuant", 64, 32, 0.1, False),
+    ("block_token", "BlockQuant", 64, 64, 0.05, "TokenQuant", 64, 32, 0.1, False),
+    ("channel128_vector", "ChannelQuant", 128, 32, 0.02, "VectorQuant", 128, 64, 0.15, False),
+    ("vector_block", "VectorQuant", 64, 32, 0.1, "BlockQuant", 64, 64, 0.05, False),
+    ("channel_token_prerope", "ChannelQuant", 64, 64, 0.05, "TokenQuant", 64, 32, 0.1, True),
+)
+UPDATE_SHAPE = dict(B=2, H=2, D=128, prefill=150, steps=45, seed=4321)
+
+
+def rope_tables(B, t0, t1, D):
+    """cos / sin [B, t1 - t0, D] as a Llama rotary embedding hands them to the attention layers."""
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    pos = torch.arange(t0, t1, dtype=torch.float32)
+    f = torch.outer(pos, inv)
+    emb = torch.cat((f, f), dim=-1)
+    return emb.cos().half()[None].expand(B, -1, -1).contiguous(), emb.sin().half()[None].expand(B, -1, -1).contiguous()
+
+
+def update_inputs():
+    """The key / value states [B, H, T, D] fed to the cache, chunk by chunk."""
+    s = UPDATE_SHAPE
+    T = s["prefill"] + s["steps"]
+    k, v = synth_kv(T, s["B"], s["H"], s["D"], s["seed"])            # [T, B, H, D]
+    k, v = k.permute(1, 2, 0, 3).contiguous(), v.permute(1, 2, 0, 3).contiguous()
+    cuts = [0, s["prefill"]] + [s["prefill"] + i + 1 for i in range(s["steps"])]
+    return k, v, cuts
+
+
+def make_update():
+    import hashlib
+    s = UPDATE_SHAPE
+    k, v, cuts = update_inputs()
+    out = {}
+    meta = []
+    for name, km, kb, kr, krel, vm, vb, vr, vrel, pre in UPDATE_CASES:
+        ck = cv = bk = bv = None
+        coss = sins = None
+        shas = []
+        for a, b in zip(cuts[:-1], cuts[1:]):
+            ks, vs = k[:, :, a:b], v[:, :, a:b]
+            cos, sin = rope_tables(s["B"], a, b, s["D"])
+            # models/cache/kvcomp_quant.py:43-75
+            if pre:
+                coss, sins = safe_cat(coss, cos, dim=1), safe_cat(sins, sin, dim=1)
+            else:
+                ks = apply_rotary_pos_emb_single(ks, cos, sin)
+            ck, bk = quant_error(ck, bk, ks, kb, kr, krel, QuantMode(km))
+            cv, bv = quant_error(cv, bv, vs, vb, vr, vrel, QuantMode(vm))
+            K, V = safe_cat(ck, bk, dim=2), safe_cat(cv, bv, dim=2)
+            if pre:
+                K = apply_rotary_pos_emb_single(K, coss, sins)
+            shas.append([hashlib.sha256(K.contiguous().numpy().tobytes()).hexdigest(),
+                         hashlib.sha256(V.contiguous().numpy().tobytes()).hexdigest()])
+        meta.append({"name": name, "k_mode": km, "k_block": kb, "k_recent": kr, "k_rel": krel, "v_mode": vm,
+                     "v_block": vb, "v_recent": vr, "v_rel": vrel, "pre_rope": pre, "sha": shas,
+                     "k_compressed": 0 if ck is None else int(ck.shape[2]), "v_compressed": 0 if cv is None else int(cv.shape[2])})
+        if name in ("channel_token", "channel_token_prerope"):
+            out[name + "_K"], out[name + "_V"] = K.contiguous().numpy(), V.contiguous().numpy()
+    out["cases_json"] = np.frombuffer(json.dumps({"cases": meta, "shape": s, "cuts": cuts}).encode(), dtype=np.uint8)
+    np.savez_compressed(os.path.join(HERE, "update_golden.npz"), **out)
+    print("update_golden.npz:", len(meta), "cases,", [(m["k_compressed"], m["v_compressed"]) for m in meta])
+
+
 if __name__ == "__main__":
+    if "--update-only" in sys.argv:
+        make_update()
+        sys.exit(0)
     make_quant()
     make_huffman()
     make_flat()
+    make_update()

@@ -2,7 +2,10 @@
 (KVCompCtx, KVCompCache), written the way the reference's own scripts exercise them
 (kvcomp_cuda_extension/scripts/test_py_ctx_k_2d_load.py, test_py_ctx_v.py, twice_get.py,
 accuracy/reproduce_cuda_error.py), with the CPU checker as the referee."""
+import hashlib
+import json
 import math
+import os
 
 import numpy as np
 import pytest
@@ -294,3 +297,176 @@ def test_evaluation_harness_keys(cfg):
     assert all(x > 1.0 for x in r["k_huffman_crs"] + r["v_huffman_crs"])
     assert all(h > q * 0.9 for h, q in zip(r["k_huffman_crs"], r["k_quant_crs"]))
     assert quant_rel_to_bit_num(0.05) == 5 and quant_rel_to_bit_num(0.1) == 4
+
+
+# ---- the model-facing cache against the reference's own update() ------------------------------------------
+def _golden_inputs(meta):
+    s, cuts = meta["shape"], meta["cuts"]
+    g = torch.Generator().manual_seed(s["seed"])
+    H, D, B, T = s["H"], s["D"], s["B"], cuts[-1]
+    mu = 0.5 * torch.randn(H, D, generator=g)
+    sd = torch.exp(0.5 * torch.randn(H, D, generator=g))
+    sd = torch.where(torch.rand(H, D, generator=g) < 0.02, 8 * sd, sd)
+    k = (mu + sd * torch.randn(T, B, H, D, generator=g)).half()
+    r = torch.exp(0.25 * torch.randn(T, B, generator=g))
+    v = (r[..., None, None] * torch.randn(T, B, H, D, generator=g)).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    f = torch.outer(torch.arange(T, dtype=torch.float32), inv)
+    emb = torch.cat((f, f), dim=-1)
+    cos = emb.cos().half()[None].expand(B, -1, -1).contiguous()
+    sin = emb.sin().half()[None].expand(B, -1, -1).contiguous()
+    return k.permute(1, 2, 0, 3).contiguous().cuda(), v.permute(1, 2, 0, 3).contiguous().cuda(), cos.cuda(), sin.cuda()
+
+
+def test_cache_update_returns_the_reference_values(cfg, golden_dir):
+    """KVCompCache.update() with a reference-style configuration (no extra fields) at batch 2: after the
+    prefill and after each of 45 single-token steps, K and V equal bit for bit what the reference's
+    update() returned (tests/golden/update_golden.npz: models/cache/kvcomp_quant.py:29-75 run on the CPU),
+    for five mode / block / recent-window / pre-RoPE settings.  V blocks of 64 tokens leave quantised
+    tokens waiting for their 128-token Huffman vector."""
+    from kvcomp_b200.cache import KVCompCache
+    z = np.load(os.path.join(golden_dir, "update_golden.npz"))
+    meta = json.loads(bytes(z["cases_json"]).decode())
+    kk, vv, cos, sin = _golden_inputs(meta)
+    s, cuts = meta["shape"], meta["cuts"]
+    for c in meta["cases"]:
+        cfg(kmode=c["k_mode"], vmode=c["v_mode"], kblk=c["k_block"], vblk=c["v_block"], krec=c["k_recent"],
+            vrec=c["v_recent"], krel=c["k_rel"], vrel=c["v_rel"], enable_pre_rope=c["pre_rope"])
+        cache = KVCompCache(s["B"], s["H"], s["D"], layer_num=1)
+        for i, (a, b) in enumerate(zip(cuts[:-1], cuts[1:])):
+            K, V = cache.update(kk[:, :, a:b], vv[:, :, a:b], 0, {"cos": cos[:, a:b], "sin": sin[:, a:b]})
+            if i in (0, 1, 20, len(cuts) - 2) or i % 7 == 0:
+                assert hashlib.sha256(K.contiguous().cpu().numpy().tobytes()).hexdigest() == c["sha"][i][0], (c["name"], "K", i)
+                assert hashlib.sha256(V.contiguous().cpu().numpy().tobytes()).hexdigest() == c["sha"][i][1], (c["name"], "V", i)
+        assert cache.k_ctx[0].compressed_ctx_len == c["k_compressed"] and cache.v_ctx[0].compressed_ctx_len == c["v_compressed"]
+        assert cache.get_seq_length(0) == cuts[-1]
+        if c["name"] + "_K" in z:
+            assert np.array_equal(K.contiguous().cpu().numpy().view(np.uint16), z[c["name"] + "_K"].view(np.uint16))
+            assert np.array_equal(V.contiguous().cpu().numpy().view(np.uint16), z[c["name"] + "_V"].view(np.uint16))
+
+
+def test_ctx_rebook_when_a_frozen_book_meets_new_symbols(cfg):
+    """A book frozen on a narrow sample, then data with symbols it has no code for: the reference drops them
+    (kernels.cu:197-205), this context re-encodes once.  Codes, get() and the fused kernels still agree with
+    the checker."""
+    from kvcomp_b200.cache import KVCompCtx
+    cfg(kmode="BlockQuant", vmode="TokenQuant", krec=0, vrec=0, krel=0.05, vrel=0.1)
+    T, B, H = 512, 1, 2
+    k, v, q = synth(T, B, H, seed=14)
+    for is_k, x, mode, blk, rel in ((True, k, orc.MODE_BLOCK, 64, 0.05), (False, v, orc.MODE_TOKEN, 128, 0.1)):
+        xd = x.cuda()
+        ctx = KVCompCtx(is_k, B, H, 128, rel)
+        narrow = (xd[:128] * 0.0 + xd[:128].mean()).half()
+        narrow[::2] += 0.5                                            # two levels only: a book of very few symbols
+        ctx.build_codebook([narrow])
+        few = ctx.book.header()["n_symbols"]
+        ctx.store(xd[:256])                                           # unseen symbols at the first store
+        assert getattr(ctx, "rebooks", 0) == 1 and ctx.book.header()["n_symbols"] > few
+        ctx.store(xd[256:])                                           # the rebuilt book covers every reachable code
+        assert ctx.rebooks == 1
+        oc = np.concatenate([orc.quant(x[i:i + 256].numpy(), mode, blk, rel, True)[0] for i in (0, 256)])
+        decoded, _ = ctx.get_decode_quant_ints()
+        assert np.array_equal(decoded.reshape(T, B, H, 128).cpu().numpy(), oc)
+        full, _ = ctx.get()
+        parts = [orc.quant(x[i:i + 256].numpy(), mode, blk, rel, True) for i in (0, 256)]
+        want = np.concatenate([orc.dequant(p[0], p[1], p[2], p[3]) for p in parts])
+        assert np.array_equal(full.cpu().numpy().view(np.uint16), want.view(np.uint16))
+        if is_k:
+            C, _ = ctx.mat_vec_mul(q.cuda())
+            ref = torch.einsum("tbhc,bhc->bht", full.float(), q.cuda().float())
+            check_error(ref, C.float(), 0.01)
+
+
+class _TinyAttention(torch.nn.Module):
+    """A minimal decoder attention layer in the shape of models/llama.py:236-308: q/k/v/o projections, rotary
+    embedding on q here and on k inside the cache, grouped-query heads, and the cache hook."""
+
+    def __init__(self, hidden, Hq, Hkv, layer_idx, seed):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        self.Hq, self.Hkv, self.D, self.layer_idx = Hq, Hkv, 128, layer_idx
+        mk = lambda o, i: torch.nn.Parameter((torch.randn(o, i, generator=g) / math.sqrt(i)).half().cuda(), requires_grad=False)
+        self.wq, self.wk, self.wv, self.wo = mk(Hq * 128, hidden), mk(Hkv * 128, hidden), mk(Hkv * 128, hidden), mk(hidden, Hq * 128)
+        self.scaling = 1.0 / math.sqrt(128)
+
+    def forward(self, x, cos, sin, cache, fused):
+        from kvcomp_b200.utils.compute import apply_rotary_pos_emb_single
+        B, t, _ = x.shape
+        q = (x @ self.wq.T).view(B, t, self.Hq, 128).transpose(1, 2)
+        k = (x @ self.wk.T).view(B, t, self.Hkv, 128).transpose(1, 2)
+        v = (x @ self.wv.T).view(B, t, self.Hkv, 128).transpose(1, 2)
+        q = apply_rotary_pos_emb_single(q, cos, sin)                    # models/llama.py:281
+        kw = {"cos": cos, "sin": sin}
+        if fused and t == 1:
+            # the hook: two lines instead of update() + eager attention (models/llama.py:283-297)
+            cache.append(k, v, self.layer_idx, kw)
+            a = cache.attend(q, self.layer_idx, self.scaling)           # [B, Hq, 1, D]
+        else:
+            K, V = cache.update(k, v, self.layer_idx, kw)               # models/llama.py:283
+            # eager_attention_forward, models/llama.py:211-234 (causal mask for the prefill)
+            g = self.Hq // self.Hkv
+            Kr, Vr = K.repeat_interleave(g, dim=1), V.repeat_interleave(g, dim=1)      # repeat_kv, :199-208
+            w = torch.matmul(q, Kr.transpose(2, 3)) * self.scaling
+            if t > 1:
+                T = K.shape[2]
+                mask = torch.full((t, T), float("-inf"), device=x.device).triu(T - t + 1)
+                w = w + mask.to(w.dtype)
+            w = torch.softmax(w, dim=-1, dtype=torch.float32).to(q.dtype)
+            a = torch.matmul(w, Vr)
+        return a.transpose(1, 2).reshape(B, t, self.Hq * 128) @ self.wo.T
+
+
+def test_two_layer_decode_loop_through_the_hook(cfg):
+    """A two-layer model decodes 600 tokens from an empty cache through append() + attend(), crossing K blocks,
+    V vectors and both recent windows, starting before anything is compressed; a twin model with the same
+    weights takes the reference's route (update() + eager attention).  The hidden states fed to both are the
+    same, so every step compares one attention layer output: fused against eager over the dequantised cache."""
+    from kvcomp_b200.cache import KVCompCache
+    cfg(kmode="ChannelQuant", vmode="TokenQuant", kblk=64, vblk=64, krec=128, vrec=256, krel=0.05, vrel=0.1)
+    B, hidden, Hq, Hkv, steps = 2, 256, 8, 2, 600
+    layers = [_TinyAttention(hidden, Hq, Hkv, i, 100 + i) for i in range(2)]
+    fused_cache, eager_cache = KVCompCache(B, Hq, 128, 2), KVCompCache(B, Hq, 128, 2)
+    cos_all, sin_all = _rope(steps + 8)
+    cos_all, sin_all = cos_all.cuda().expand(B, -1, -1), sin_all.cuda().expand(B, -1, -1)
+    g = torch.Generator().manual_seed(7)
+    worst = 0.0
+    pos = 0
+    for step in range(steps):
+        t = 5 if step == 0 else 1                                        # a short prompt, then one token at a time
+        x = torch.randn(B, t, hidden, generator=g).half().cuda()
+        cos, sin = cos_all[:, pos:pos + t], sin_all[:, pos:pos + t]
+        hf = he = x
+        for layer in layers:
+            of = layer(hf, cos, sin, fused_cache, fused=True)
+            oe = layer(he, cos, sin, eager_cache, fused=False)
+            err = (of.float() - oe.float()).abs().max().item() / max(oe.float().abs().max().item(), 1e-6)
+            worst = max(worst, err)
+            assert err <= 4e-3, (step, layer.layer_idx, err)             # two fp16 matmuls sit on top of the attention's 1e-3
+            hf = he = (x + oe).half()                                    # both models continue from the same state
+        pos += t
+    fused_cache.check()
+    for l in range(2):
+        assert fused_cache.get_seq_length(l) == eager_cache.get_seq_length(l) == pos
+        assert fused_cache.k_ctx[l].encoded_ctx_len >= 384 and fused_cache.v_ctx[l].encoded_ctx_len >= 256
+    assert worst > 0.0
+
+
+def test_attend_pre_rope_and_plain(cfg):
+    """attend() also answers for caches the fused kernel cannot read directly: pre-RoPE keys (stored
+    unrotated, rotated on the way out) and caches with quantisation switched off."""
+    from kvcomp_b200.cache import KVCompCache
+    B, Hkv, Hq, T = 1, 2, 4, 300
+    k, v, q = synth(T, B, Hkv, seed=15, Hq=Hq)
+    kk, vv = k.permute(1, 2, 0, 3).contiguous().cuda(), v.permute(1, 2, 0, 3).contiguous().cuda()
+    cos, sin = _rope(T)
+    kw = {"cos": cos.cuda(), "sin": sin.cuda()}
+    qd = q.cuda().unsqueeze(2)
+    for kwargs in (dict(enable_pre_rope=True, krec=64, vrec=64), dict(enable_quant=False)):
+        cfg(kmode="ChannelQuant", **kwargs)
+        cache = KVCompCache(B, Hq, 128, 1)
+        K, V = cache.update(kk, vv, 0, kw)
+        out = cache.attend(qd, 0)
+        g = Hq // Hkv
+        w = torch.softmax(torch.matmul(qd.float(), K.float().repeat_interleave(g, 1).transpose(2, 3)) / math.sqrt(128), dim=-1)
+        ref = torch.matmul(w, V.float().repeat_interleave(g, 1))
+        assert out.shape == (B, Hq, 1, 128) and (out.float() - ref).abs().max() <= 2e-3 * ref.abs().max()

@@ -13,7 +13,19 @@ from oracle import kvc_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-ATTN_RTOL = 1e-3      # relative to max |out|; the tolerance BASELINE.json's north_star states
+ATTN_RTOL = 1e-3      # relative to max |out|: the 1e-3 relative error the path's specification states
+ATTN_ELEM_RTOL = 2e-3  # per element, on top of a floor of 2e-4 of max |out| (the output is rounded to fp16: 2^-11)
+
+
+def assert_attn_close(out, O, what=""):
+    """out: the kernel's fp16 output; O: the checker's exact (double precision) attention over the
+    dequantised values (code + min_int) * scale.  Two bounds: every element within ATTN_RTOL of the largest
+    output magnitude, and every element within ATTN_ELEM_RTOL of its own magnitude plus a small floor."""
+    got = out.float().cpu().numpy()
+    err = np.abs(got - O)
+    top = np.abs(O).max()
+    assert err.max() <= ATTN_RTOL * top, (what, err.max() / top)
+    assert (err <= ATTN_ELEM_RTOL * np.abs(O) + 2e-4 * top).all(), (what, (err / (np.abs(O) + 1e-30)).max())
 
 
 @pytest.fixture(scope="module")
@@ -399,13 +411,162 @@ def test_attn_decode(ops, kmode, vmode, shared, T, B, Hkv, Hq, Tr, splits, min_d
     ko = _oracle_q(rk, T, B, Hkv, kmode, 64, shared)
     vo = _oracle_q(rv, T, B, Hkv, vmode, 128, shared)
     O = orc.attention(*ko, *vo, q, scaling, k[T:] if Tr else None, v[T:] if Tr else None)
-    err = np.abs(out.float().cpu().numpy() - O).max() / np.abs(O).max()
-    assert err <= ATTN_RTOL, err
+    assert_attn_close(out, O)
     # a second call reuses a caller-held workspace and must give the same bits
     ws = ops.attn_workspace(B, Hq, max(splits, ops.attn_splits(T, B, Hkv)), "cuda")
     o1, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
     o2, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
     assert torch.equal(o1, o2) and torch.equal(o1, out)
+
+
+@pytest.mark.parametrize("B,Hkv,Hq,T,Tr", [(2, 2, 8, 1024, 0), (1, 2, 10, 768, 45), (3, 10, 40, 256, 0)])
+def test_attn_decode_phi3_settings(ops, B, Hkv, Hq, T, Tr):
+    """The Phi-3-medium-shaped configuration's settings: K per channel in 128-token blocks at relative error
+    bound 0.02 (about 52 symbols, 5.5 bits each), V per token at 0.15, four query heads per KV head -- and
+    five per KV head, which the kernel handles as chunks of 4 + 1."""
+    k, v, q = synth(T + Tr, B, Hkv, seed=33, Hq=Hq)
+    rk, rv, kc, vc = _caches(ops, k[:T], v[:T], orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.02, 0.15, 128, False)
+    assert rk["book"].header()["n_symbols"] >= 45 and rk["book"].header()["escape"] in (0, 1)
+    scaling = 1.0 / math.sqrt(128)
+    kt = dev(k[T:]) if Tr else None
+    vt = dev(v[T:]) if Tr else None
+    out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt)
+    assert ops.read_status(st) == 0
+    O = orc.attention(*_oracle_q(rk, T, B, Hkv, orc.MODE_CHANNEL, 128, False),
+                      *_oracle_q(rv, T, B, Hkv, orc.MODE_TOKEN, 128, False), q, scaling,
+                      k[T:] if Tr else None, v[T:] if Tr else None)
+    assert_attn_close(out, O)
+
+
+def test_attn_decode_llama7b_shape_small(ops):
+    """The Llama-2-7B-shaped configuration with a short context: batch 8, 32 heads (MHA), K per channel
+    at 0.05, V per token at 0.1, block 64."""
+    T, B, H = 512, 8, 32
+    k, v, q = synth(T, B, H, seed=44)
+    rk, rv, kc, vc = _caches(ops, k, v, orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.05, 0.1, 64, False)
+    scaling = 1.0 / math.sqrt(128)
+    out, st = ops.attn_decode(kc, vc, T, B, H, dev(q), scaling)
+    assert ops.read_status(st) == 0
+    O = orc.attention(*_oracle_q(rk, T, B, H, orc.MODE_CHANNEL, 64, False),
+                      *_oracle_q(rv, T, B, H, orc.MODE_TOKEN, 128, False), q, scaling)
+    assert_attn_close(out, O)
+
+
+def _skewed_cache(ops, rng, is_k, T, B, H):
+    """Codes drawn from a very skewed alphabet (a code longer than the 12-bit decode window exists), with
+    made-up units: K per 64-token block and sequence, V per token and sequence."""
+    p = np.array([2.0 ** -(i + 1) for i in range(20)]); p[-1] = p[-2]; p /= p.sum()
+    p[12:] = p[12:].sum() / 8
+    codes = rng.choice(20, size=(T, B, H, 128), p=p / p.sum()).astype(np.uint8)
+    codes[1, 0, 0, :20] = np.arange(20)
+    mode, blk = (orc.MODE_BLOCK, 64) if is_k else (orc.MODE_TOKEN, 128)
+    m, n = orc.qmeta(mode, False, T, B, H, 128, blk)
+    mi = rng.integers(-12, 3, n).astype(np.int16)
+    sc = (0.02 + 0.1 * rng.random(n)).astype(np.float16)
+    spec = ops.qspec(mode, False, B, H, 128, blk)
+    cd = dev(codes)
+    book = ops.build_codebook(ops.histogram(cd.view(-1)))
+    bsz, tsz, _, cap = ops.buffer_sizes(T, B * H * 128, is_k)
+    bi = torch.zeros(bsz, dtype=torch.uint8, device="cuda")
+    ti = torch.zeros(tsz // 2, dtype=torch.int16, device="cuda")
+    enc = torch.zeros(cap, dtype=torch.uint8, device="cuda")
+    total, st = ops.encode(cd, is_k, book.encode_table(), bi, ti, enc)
+    assert ops.read_status(st) & ~0x10 == 0
+    n_bytes, maxb = (int(x) for x in total.tolist())
+    mid, scd = dev(mi), dev(sc)
+    cache = ops.make_cache(enc, bi, ti, book, mid, scd, spec, n_bytes, maxb)
+    return cache, (enc, bi, ti, book, mid, scd), (codes, mi, sc, m), book
+
+
+@pytest.mark.parametrize("G", [1, 2, 4, 3])
+def test_attn_decode_books_with_long_codes(ops, G):
+    """Books whose header says `escape`: the fused kernels take the decoder that tests every table entry and
+    continues bit by bit from the tree, for one, two and four query heads per KV head (and 3 = 2 + 1)."""
+    rng = np.random.default_rng(5 + G)
+    T, B, Hkv = 512, 2, 2
+    Hq = Hkv * G
+    kc, keep_k, ko, kbook = _skewed_cache(ops, rng, True, T, B, Hkv)
+    vc, keep_v, vo, vbook = _skewed_cache(ops, rng, False, T, B, Hkv)
+    for b in (kbook, vbook):
+        hd = b.header()
+        assert hd["escape"] == 1 and hd["max_len"] > 12
+    q = (rng.standard_normal((B, Hq, 128)) / math.sqrt(128)).astype(np.float16)
+    scaling = 1.0 / math.sqrt(128)
+    out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=2)
+    assert ops.read_status(st) == 0
+    O = orc.attention(*ko, *vo, q, scaling)
+    assert_attn_close(out, O)
+    # the two-call kernels take the same path
+    S, st = ops.fused_qk(kc, T, B, Hkv, dev(q), out_dtype=torch.float32)
+    assert ops.read_status(st) == 0
+    So = orc.qk(*ko, q)
+    assert np.abs(S.cpu().numpy() - So).max() <= 5e-4 * np.abs(So).max()
+
+
+def test_attn_decode_flags_a_vector_that_starts_outside_its_block(ops):
+    """thread_info is input: an entry that points past its block's bytes (still inside the staging area) must
+    be reported, not decoded."""
+    T, B, Hkv, Hq = 512, 1, 2, 2
+    k, v, q = synth(T, B, Hkv, seed=51, Hq=Hq)
+    rk, rv, kc, vc = _caches(ops, k, v, orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.05, 0.1, 64, False)
+    scaling = 1.0 / math.sqrt(128)
+    out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling)
+    assert ops.read_status(st) == 0
+    for r, is_k in ((rk, True), (rv, False)):
+        ti = r["ti"].clone()
+        bad = r["ti"].clone()
+        # vector 10 of block 3 would start 40 bytes past the largest block
+        bad[64 * 3 + 9] = int(np.array([(r["maxb"] + 40) << 3], dtype=np.uint16).view(np.int16)[0])
+        r["ti"].copy_(bad)
+        out2, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling)
+        assert ops.read_status(st, raise_on_fatal=False) & 0x80, "K" if is_k else "V"
+        assert torch.isfinite(out2.float()).all()
+        if is_k:
+            S, st = ops.fused_qk(kc, T, B, Hkv, dev(q))
+        else:
+            P = torch.softmax(torch.randn(B, Hq, T, device="cuda"), dim=-1).half()
+            S, st = ops.fused_pv(vc, T, B, Hkv, P)
+        assert ops.read_status(st, raise_on_fatal=False) & 0x80
+        r["ti"].copy_(ti)
+    out3, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling)
+    assert ops.read_status(st) == 0 and torch.equal(out3, out)
+
+
+def test_attn_decode_staging_wait_runs_out_and_returns(ops):
+    """The kernel's waits for its staged blocks are bounded.  With the diagnostic that announces bytes which
+    are never copied, the first wait runs out after a few tries: the call returns, the status word carries
+    KVC_FLAG_WAIT_TIMEOUT, nothing is left in flight, and the next ordinary call is correct."""
+    T, B, Hkv, Hq = 512, 2, 2, 4
+    k, v, q = synth(T, B, Hkv, seed=52, Hq=Hq)
+    rk, rv, kc, vc = _caches(ops, k, v, orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.05, 0.1, 64, False)
+    scaling = 1.0 / math.sqrt(128)
+    want, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=2)
+    assert ops.read_status(st) == 0
+    ws = ops.attn_workspace(B, Hq, 2, "cuda")
+    try:
+        ops.attn_debug(wait_limit=8, starve=True)
+        out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=2, workspace=ws)
+        torch.cuda.synchronize()
+        assert ops.read_status(st, raise_on_fatal=False) & 0x400
+    finally:
+        ops.attn_debug()
+    assert int(ws[:256].view(torch.int32).abs().sum()) == 0          # the scheduling counters were left zeroed
+    out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=2, workspace=ws)
+    assert ops.read_status(st) == 0 and torch.equal(out, want)
+
+
+def test_attn_decode_tail_only(ops):
+    """Nothing compressed yet (the first tokens of a sequence): T = 0, no streams, only fp16 rows."""
+    B, Hkv, Hq, Tr = 2, 2, 6, 77
+    k, v, q = synth(Tr, B, Hkv, seed=53, Hq=Hq)
+    scaling = 1.0 / math.sqrt(128)
+    out, st = ops.attn_decode(None, None, 0, B, Hkv, dev(q), scaling, dev(k), dev(v))
+    assert ops.read_status(st) == 0
+    kf, vf = torch.from_numpy(k).float(), torch.from_numpy(v).float()
+    g = Hq // Hkv
+    S = torch.einsum("bhd,tbhd->bht", torch.from_numpy(q).float(), kf.repeat_interleave(g, dim=2)) * scaling
+    O = torch.einsum("bht,tbhd->bhd", torch.softmax(S.double(), -1).float(), vf.repeat_interleave(g, dim=2)).numpy()
+    assert_attn_close(out, O)
 
 
 def test_attn_decode_many_items(ops):
@@ -422,8 +583,7 @@ def test_attn_decode_many_items(ops):
     for splits, w in ((8, ws), (8, ws), (1, False), (1, ws), (0, None), (3, None)):
         out, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=splits, workspace=w)
         assert ops.read_status(st) == 0
-        err = np.abs(out.float().cpu().numpy() - O).max() / np.abs(O).max()
-        assert err <= ATTN_RTOL, (splits, err)
+        assert_attn_close(out, O, splits)
         outs.append(out)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[2], outs[3])
     assert int(ws[:256].view(torch.int32).abs().sum()) == 0
@@ -461,7 +621,7 @@ def test_attn_decode_config0(ops):
     assert ops.read_status(st) == 0
     O = orc.attention(*_oracle_q(rk, T, B, H, orc.MODE_CHANNEL, 64, False),
                       *_oracle_q(rv, T, B, H, orc.MODE_TOKEN, 128, False), q, scaling)
-    assert np.abs(out.float().cpu().numpy() - O).max() <= ATTN_RTOL * np.abs(O).max()
+    assert_attn_close(out, O)
     # the two-call path (scores -> softmax -> partials) agrees as well
     S, _ = ops.fused_qk(kc, T, B, H, dev(q), out_dtype=torch.float32)
     P = torch.softmax(S * scaling, dim=-1).half()

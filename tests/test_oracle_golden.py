@@ -173,3 +173,64 @@ def test_attention_pieces_consistent(qg):
     P3 = np.exp(S3 - S3.max(-1, keepdims=True)); P3 /= P3.sum(-1, keepdims=True)
     O3 = np.einsum("bht,tbhd->bhd", P3, vh)
     assert np.abs(O2 - O3).max() < 2e-3 * np.abs(O3).max()
+
+
+def _rope_cpu(t, cos, sin):
+    """utils/compute.py:25-33 on [B, H, t, D] fp16 tensors (torch on the CPU: every op rounds to fp16)."""
+    import torch
+    cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+    half = t.shape[-1] // 2
+    rot = torch.cat((-t[..., half:], t[..., :half]), dim=-1)
+    return (t * cos) + (rot * sin)
+
+
+def test_model_path_update_matches_reference(golden_dir):
+    """What the reference's model-facing cache returns from update() (models/cache/kvcomp_quant.py:29-75 with
+    utils/compute.py:quant_error) over a prefill and 45 single-token steps at batch 2, restated with the
+    checker's quantiser, dequantiser and block cutter: units per sequence, min_ints not narrowed."""
+    import hashlib
+    import torch
+    z = np.load(os.path.join(golden_dir, "update_golden.npz"))
+    meta = json.loads(bytes(z["cases_json"]).decode())
+    s, cuts = meta["shape"], meta["cuts"]
+    g = torch.Generator().manual_seed(s["seed"])
+    H, D, B, T = s["H"], s["D"], s["B"], cuts[-1]
+    mu = 0.5 * torch.randn(H, D, generator=g)
+    sd = torch.exp(0.5 * torch.randn(H, D, generator=g))
+    sd = torch.where(torch.rand(H, D, generator=g) < 0.02, 8 * sd, sd)
+    k = (mu + sd * torch.randn(T, B, H, D, generator=g)).half()
+    r = torch.exp(0.25 * torch.randn(T, B, generator=g))
+    v = (r[..., None, None] * torch.randn(T, B, H, D, generator=g)).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    f = torch.outer(torch.arange(T, dtype=torch.float32), inv)
+    emb = torch.cat((f, f), dim=-1)
+    cos, sin = emb.cos().half()[None].expand(B, -1, -1), emb.sin().half()[None].expand(B, -1, -1)
+    for c in meta["cases"]:
+        kin = k.permute(1, 2, 0, 3)                                   # [B, H, T, D]
+        if not c["pre_rope"]:
+            kin = torch.cat([_rope_cpu(kin[:, :, a:b], cos[:, a:b], sin[:, a:b]) for a, b in zip(cuts[:-1], cuts[1:])], dim=2)
+        streams = {}
+        for tag, x, mode, blk, rec, rel in (("k", kin.permute(2, 0, 1, 3).contiguous().numpy(), c["k_mode"], c["k_block"], c["k_recent"], c["k_rel"]),
+                                            ("v", v.numpy(), c["v_mode"], c["v_block"], c["v_recent"], c["v_rel"])):
+            done, outs = 0, []                                        # tokens quantised so far
+            xh = np.zeros_like(x)
+            for b_ in cuts[1:]:
+                n = orc.cut_len(b_ - done, blk, rec)
+                if n:
+                    codes, mi, sc, m, deg = orc.quant(x[done:done + n], MODE[mode], blk, rel, False)
+                    assert deg == 0
+                    xh[done:done + n] = orc.dequant(codes, mi, sc, m)
+                    done += n
+                outs.append(np.concatenate([xh[:done], x[done:b_]], axis=0))
+            streams[tag] = outs
+            assert done == c[tag + "_compressed"]
+        for i, b_ in enumerate(cuts[1:]):
+            K = torch.from_numpy(streams["k"][i]).permute(1, 2, 0, 3)
+            V = torch.from_numpy(streams["v"][i]).permute(1, 2, 0, 3).contiguous()
+            if c["pre_rope"]:
+                K = _rope_cpu(K, cos[:, :b_], sin[:, :b_])
+            K = K.contiguous()
+            assert hashlib.sha256(K.numpy().tobytes()).hexdigest() == c["sha"][i][0], (c["name"], "K", i)
+            assert hashlib.sha256(V.numpy().tobytes()).hexdigest() == c["sha"][i][1], (c["name"], "V", i)
+        if c["name"] + "_K" in z:
+            assert np.array_equal(K.numpy().view(np.uint16), z[c["name"] + "_K"].view(np.uint16))

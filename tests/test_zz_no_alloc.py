@@ -63,6 +63,26 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         ops.attn_decode_static(kc, vc, T, B, Hkv, qd, scaling, got2, ktail, vtail, status=status)
         want2, _ = ops.attn_decode(kc, vc, T, B, Hkv, qd, scaling, ktail, vtail)
         assert ops.read_status(status) == 0 and torch.equal(got2, want2)
+    # against the CPU checker as well, not only against the library's other entry point
+    import numpy as np
+    from oracle import kvc_oracle as orc
+    kq = orc.quant(k[:T].cpu().numpy(), orc.MODE_CHANNEL, 64, 0.05, False)[:4]
+    vq = orc.quant(v[:T].cpu().numpy(), orc.MODE_TOKEN, 128, 0.1, False)[:4]
+    O = orc.attention(*kq, *vq, qd.cpu().numpy(), scaling, ktail.cpu().numpy(), vtail.cpu().numpy())
+    assert np.abs(got.float().cpu().numpy() - O).max() <= 1e-3 * np.abs(O).max()
+    # more splits than a column has tiles: the split count is clamped before the scratch is sized, so a
+    # request like 256 heads x 64 splits over 4 tiles fits (it needs about 1 MB, not 17)
+    Tb, Bb, Hb = 1024, 8, 32
+    kb, vb, qb = make_kv(Tb, Bb, Hb, 128, seed=78, device="cpu")
+    kcb, keep_kb = _cache(ops, kb.cuda(), True, ops.MODE_CHANNEL, 0.05)
+    vcb, keep_vb = _cache(ops, vb.cuda(), False, ops.MODE_TOKEN, 0.1)
+    gotb = torch.empty((Bb, Hb, 128), dtype=torch.float16, device="cuda")
+    qbd = qb.cuda()
+    rc = lib.kvc_attn_decode_static(C.byref(kcb), C.byref(vcb), Tb, Bb, Hb, Hb, p(qbd), scaling, None, None, 0,
+                                    p(gotb), 64, p(status), stream)
+    assert rc == 0, lib.kvc_last_error()
+    wantb, _ = ops.attn_decode(kcb, vcb, Tb, Bb, Hb, qbd, scaling, splits=64)
+    assert ops.read_status(status) == 0 and torch.equal(gotb, wantb)
     # a request whose scratch does not fit the built-in array is refused with a clear error
     rc = lib.kvc_attn_decode_static(C.byref(kc), C.byref(vc), T, 4096, Hkv, 4096 * 4, p(qd), scaling, None, None, 0,
                                     p(got), 4, p(status), stream)
