@@ -136,6 +136,21 @@ int kvc_quantize(const void *x, int64_t T, int64_t B, int64_t H, int64_t D,
                  unsigned long long *hist, void *workspace, int64_t workspace_bytes,
                  int32_t *status, kvc_stream_t stream);
 
+/* The quantiser in two calls, for caches whose KV heads are split over several GPUs.  BlockQuant and
+ * TokenQuant units span the heads (models/cache/kvcomp_encode.py:10-13, utils/compute.py:138-143), so a
+ * rank that holds some of the heads cannot derive scale and min_int alone.  kvc_quant_minmax writes the
+ * extremes of this rank's x per unit (device fp16 mn_out[units], mx_out[units], units as in
+ * kvc_qmeta_make); the ranks take the elementwise minimum / maximum over all of them; kvc_quantize_ranged
+ * then quantises x with the given extremes.  One rank holding every head gets the bits of kvc_quantize.
+ * Other modes are refused: their units are local to a head.  workspace: 8 bytes per unit. */
+int kvc_quant_minmax(const void *x, int64_t T, int64_t B, int64_t H, int64_t D, int mode, int batch_shared,
+                     int64_t block, void *mn_out, void *mx_out, void *workspace, int64_t workspace_bytes,
+                     kvc_stream_t stream);
+int kvc_quantize_ranged(const void *x, int64_t T, int64_t B, int64_t H, int64_t D, int mode, int batch_shared,
+                        int64_t block, float rel, const void *mn_in, const void *mx_in,
+                        uint8_t *codes, void *min_int, int min_bytes, void *scale, unsigned long long *hist,
+                        void *workspace, int64_t workspace_bytes, int32_t *status, kvc_stream_t stream);
+
 /* (codes + min_int) * scale -> fp16 (models/cache/kvcomp_encode.py:146). */
 int kvc_dequant(const uint8_t *codes, const kvc_qmeta *q, int64_t T, int64_t B, int64_t H, int64_t D,
                 void *out, kvc_stream_t stream);

@@ -58,6 +58,9 @@ _SIGNATURES = {
     "kvc_quantize_workspace": (_i64, [_i32, _i32, _i64, _i64, _i64]),
     "kvc_quantize": (_i32, [_vp, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _f32, _vp, _vp, _i32, _vp, _vp,
                             _vp, _i64, _vp, _vp]),
+    "kvc_quant_minmax": (_i32, [_vp, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "kvc_quantize_ranged": (_i32, [_vp, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _f32, _vp, _vp, _vp, _vp, _i32, _vp,
+                                   _vp, _vp, _i64, _vp, _vp]),
     "kvc_dequant": (_i32, [_vp, C.POINTER(QMeta), _i64, _i64, _i64, _i64, _vp, _vp]),
     "kvc_histogram": (_i32, [_vp, _i64, _vp, _vp]),
     "kvc_build_codebook": (_i32, [_vp, _vp, _vp]),

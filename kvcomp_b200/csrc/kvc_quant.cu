@@ -285,6 +285,8 @@ __global__ void __launch_bounds__(WARPS == 1 ? 256 : WARPS * 32) quant_contig_re
 // ---- BlockQuant: one unit per token block (x sequence), far larger than a CTA ------------------
 // Three launches: per-row min/max folded into the unit with atomics on order-preserving keys,
 // a per-unit finalise, and the elementwise pass.  A row is one (token, b): H*D contiguous values.
+// The same three serve the two-call form (kvc_quant_minmax / kvc_quantize_ranged) for every unit made of
+// whole rows: `blk` is then the unit's token divisor (the block for BlockQuant, 1 for TokenQuant).
 __device__ __forceinline__ unsigned int half_key(float f) {      // monotone in the value
     unsigned int h = __half_as_ushort(__float2half_rn(f));
     return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
@@ -318,12 +320,25 @@ __global__ void __launch_bounds__(256) quant_block_minmax_kernel(
     }
 }
 
-__global__ void quant_block_finalize_kernel(unsigned int *__restrict__ ws, long long n_units, float rel,
-                                            void *__restrict__ min_int, int min_bytes,
-                                            __half *__restrict__ scale, int *__restrict__ status) {
+// keys -> the units' extremes as fp16 (what ranks exchange when a unit spans the heads of several of them)
+__global__ void quant_minmax_export_kernel(const unsigned int *__restrict__ ws, long long n_units,
+                                           __half *__restrict__ mn_out, __half *__restrict__ mx_out) {
     long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (u >= n_units) return;
-    float mn = key_half(0xffffu - ws[2 * u]), mx = key_half(ws[2 * u + 1]);
+    mn_out[u] = __float2half_rn(key_half(0xffffu - ws[2 * u]));
+    mx_out[u] = __float2half_rn(key_half(ws[2 * u + 1]));
+}
+
+// mn_in / mx_in (optional): the units' extremes given by the caller instead of the keys in ws
+__global__ void quant_block_finalize_kernel(unsigned int *__restrict__ ws, long long n_units, float rel,
+                                            void *__restrict__ min_int, int min_bytes,
+                                            __half *__restrict__ scale, int *__restrict__ status,
+                                            const __half *__restrict__ mn_in, const __half *__restrict__ mx_in) {
+    long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= n_units) return;
+    float mn, mx;
+    if (mn_in) { mn = __half2float(mn_in[u]); mx = __half2float(mx_in[u]); }
+    else { mn = key_half(0xffffu - ws[2 * u]); mx = key_half(ws[2 * u + 1]); }
     int flags = 0;
     __half sc;
     UnitParam p = unit_param(mn, mx, rel, &sc, &flags);
@@ -490,7 +505,7 @@ extern "C" int kvc_quantize(const void *x, int64_t T, int64_t B, int64_t H, int6
         unsigned int *ws = reinterpret_cast<unsigned int *>(workspace);
         KVC_CUDA_OK(cudaMemsetAsync(ws, 0, n_units * 8, s));
         quant_block_minmax_kernel<<<(unsigned)(T * B), 256, 0, s>>>(xh, B, H * D, (int)block, batch_shared, ws);
-        quant_block_finalize_kernel<<<(unsigned)((n_units + 127) / 128), 128, 0, s>>>(ws, n_units, rel, min_int, min_bytes, sc, status);
+        quant_block_finalize_kernel<<<(unsigned)((n_units + 127) / 128), 128, 0, s>>>(ws, n_units, rel, min_int, min_bytes, sc, status, nullptr, nullptr);
         quant_block_apply_kernel<<<(unsigned)(T * B), 256, 0, s>>>(xh, B, H * D, (int)block, batch_shared, ws, codes, hist, status);
         break;
     }
@@ -521,6 +536,66 @@ extern "C" int kvc_k_matvec(const void *k, const void *q, void *out, int64_t ctx
     if (rows == 0) return KVC_OK;
     k_matvec_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, kvc_cu(stream)>>>(
         reinterpret_cast<const __half *>(k), reinterpret_cast<const __half *>(q), reinterpret_cast<__half *>(out), rows, H);
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}
+
+// ---- the quantiser in two calls: extremes first, codes later --------------------------------------
+// For units made of whole (token, sequence) rows -- BlockQuant and TokenQuant, whose units span the heads
+// (models/cache/kvcomp_encode.py:10-13, utils/compute.py:138-143).  When the heads of a cache are split
+// over several GPUs, every rank takes the extremes of its own heads, the ranks exchange them (elementwise
+// min and max), and every rank quantises with the joint extremes: same scale, min_int and codes as one GPU
+// holding all heads would produce.
+static int ranged_units(int mode, int batch_shared, int64_t T, int64_t B, int64_t block, long long *n_units, int *tok_div) {
+    KVC_REQUIRE(mode == KVC_MODE_BLOCK || mode == KVC_MODE_TOKEN, "units of mode %d do not span heads: use kvc_quantize", mode);
+    if (mode == KVC_MODE_BLOCK) KVC_REQUIRE(block > 0 && T % block == 0, "T=%lld is not a multiple of block=%lld", (long long)T, (long long)block);
+    *tok_div = mode == KVC_MODE_BLOCK ? (int)block : 1;
+    *n_units = (T / *tok_div) * (batch_shared ? 1 : B);
+    return KVC_OK;
+}
+
+extern "C" int kvc_quant_minmax(const void *x, int64_t T, int64_t B, int64_t H, int64_t D, int mode, int batch_shared,
+                                int64_t block, void *mn_out, void *mx_out, void *workspace, int64_t workspace_bytes,
+                                kvc_stream_t stream) {
+    KVC_REQUIRE(x && mn_out && mx_out, "kvc_quant_minmax: null pointer");
+    KVC_REQUIRE(T >= 0 && B > 0 && H > 0 && D > 0 && (H * D) % 8 == 0, "kvc_quant_minmax: bad shape");
+    KVC_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, "kvc_quant_minmax: x must be 16-byte aligned");
+    long long n_units; int tok_div;
+    if (int rc = ranged_units(mode, batch_shared, T, B, block, &n_units, &tok_div)) return rc;
+    if (T == 0) return KVC_OK;
+    KVC_REQUIRE(workspace && workspace_bytes >= n_units * 8, "kvc_quant_minmax: needs %lld bytes of workspace", n_units * 8);
+    KVC_REQUIRE(T * B < (1ll << 31), "kvc_quant_minmax: too many rows");
+    cudaStream_t s = kvc_cu(stream);
+    unsigned int *ws = reinterpret_cast<unsigned int *>(workspace);
+    KVC_CUDA_OK(cudaMemsetAsync(ws, 0, n_units * 8, s));
+    quant_block_minmax_kernel<<<(unsigned)(T * B), 256, 0, s>>>(reinterpret_cast<const __half *>(x), B, H * D, tok_div, batch_shared, ws);
+    quant_minmax_export_kernel<<<(unsigned)((n_units + 127) / 128), 128, 0, s>>>(ws, n_units, reinterpret_cast<__half *>(mn_out),
+                                                                                  reinterpret_cast<__half *>(mx_out));
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}
+
+extern "C" int kvc_quantize_ranged(const void *x, int64_t T, int64_t B, int64_t H, int64_t D, int mode, int batch_shared,
+                                   int64_t block, float rel, const void *mn_in, const void *mx_in,
+                                   uint8_t *codes, void *min_int, int min_bytes, void *scale, unsigned long long *hist,
+                                   void *workspace, int64_t workspace_bytes, int32_t *status, kvc_stream_t stream) {
+    KVC_REQUIRE(x && mn_in && mx_in && codes && min_int && scale && status, "kvc_quantize_ranged: null pointer");
+    KVC_REQUIRE(T >= 0 && B > 0 && H > 0 && D > 0 && (H * D) % 8 == 0, "kvc_quantize_ranged: bad shape");
+    KVC_REQUIRE(min_bytes == 1 || min_bytes == 2, "kvc_quantize_ranged: min_bytes must be 1 or 2");
+    KVC_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(codes) & 7) == 0,
+                "kvc_quantize_ranged: x must be 16-byte and codes 8-byte aligned");
+    long long n_units; int tok_div;
+    if (int rc = ranged_units(mode, batch_shared, T, B, block, &n_units, &tok_div)) return rc;
+    if (T == 0) return KVC_OK;
+    KVC_REQUIRE(workspace && workspace_bytes >= n_units * 8, "kvc_quantize_ranged: needs %lld bytes of workspace", n_units * 8);
+    KVC_REQUIRE(T * B < (1ll << 31), "kvc_quantize_ranged: too many rows");
+    cudaStream_t s = kvc_cu(stream);
+    unsigned int *ws = reinterpret_cast<unsigned int *>(workspace);
+    quant_block_finalize_kernel<<<(unsigned)((n_units + 127) / 128), 128, 0, s>>>(
+        ws, n_units, rel, min_int, min_bytes, reinterpret_cast<__half *>(scale), status,
+        reinterpret_cast<const __half *>(mn_in), reinterpret_cast<const __half *>(mx_in));
+    quant_block_apply_kernel<<<(unsigned)(T * B), 256, 0, s>>>(reinterpret_cast<const __half *>(x), B, H * D, tok_div, batch_shared,
+                                                               ws, codes, hist, status);
     KVC_LAUNCH_OK();
     return KVC_OK;
 }

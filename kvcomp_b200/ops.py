@@ -113,6 +113,50 @@ def quantize(x, mode, block, rel, batch_shared=True, min_dtype=torch.int8, hist=
     return codes, min_int, scale, spec, status
 
 
+def quant_minmax(x, mode, block, batch_shared=True):
+    """Per-unit extremes of x (fp16 [T,B,H,D]) for BlockQuant / TokenQuant units: (min fp16 [units], max
+    fp16 [units], QSpec).  First half of the two-call quantiser (kvc_quant_minmax)."""
+    lib = _lib.load()
+    _cuda(x, torch.float16, "x")
+    T, B, H, D = x.shape
+    spec = qspec(mode, batch_shared, B, H, D, block)
+    n = spec.units(T, B, H, D)
+    mn = torch.empty(n, dtype=torch.float16, device=x.device)
+    mx = torch.empty(n, dtype=torch.float16, device=x.device)
+    ws = torch.empty(max(8 * n, 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.kvc_quant_minmax(_p(x), T, B, H, D, mode, int(batch_shared), block, _p(mn), _p(mx), _p(ws),
+                                        ws.numel(), _stream()), "kvc_quant_minmax")
+    return mn, mx, spec
+
+
+def quantize_ranged(x, mode, block, rel, mn, mx, batch_shared=True, min_dtype=torch.int8, hist=None, status=None):
+    """Second half: quantise x with the given per-unit extremes (the joint ones of all head shards).
+    Returns what quantize returns."""
+    lib = _lib.load()
+    _cuda(x, torch.float16, "x")
+    _cuda(mn, torch.float16, "mn")
+    _cuda(mx, torch.float16, "mx")
+    T, B, H, D = x.shape
+    spec = qspec(mode, batch_shared, B, H, D, block)
+    n = spec.units(T, B, H, D)
+    if mn.numel() != n or mx.numel() != n:
+        raise KvcError("extremes must hold %d units" % n)
+    dev = x.device
+    codes = torch.empty((T, B, H, D), dtype=torch.uint8, device=dev)
+    min_int = torch.empty(n, dtype=min_dtype, device=dev)
+    scale = torch.empty(n, dtype=torch.float16, device=dev)
+    status = new_status(dev) if status is None else status
+    ws = torch.empty(max(8 * n, 16), dtype=torch.uint8, device=dev)
+    if hist is not None:
+        _cuda(hist, torch.int64, "hist")
+    with torch.cuda.device(dev):
+        _lib.check(lib.kvc_quantize_ranged(_p(x), T, B, H, D, mode, int(batch_shared), block, float(rel), _p(mn), _p(mx),
+                                           _p(codes), _p(min_int), min_int.element_size(), _p(scale), _p(hist), _p(ws),
+                                           ws.numel(), _p(status), _stream()), "kvc_quantize_ranged")
+    return codes, min_int, scale, spec, status
+
+
 def dequant(codes, min_int, scale, spec, out=None):
     lib = _lib.load()
     _cuda(codes, torch.uint8, "codes")

@@ -630,6 +630,74 @@ def test_attn_decode_config0(ops):
     assert np.abs(O2 - O).max() <= 2e-3 * np.abs(O).max()
 
 
+@pytest.mark.parametrize("kmode,vmode,shared", [(orc.MODE_BLOCK, orc.MODE_TOKEN, True), (orc.MODE_BLOCK, orc.MODE_TOKEN, False),
+                                                (orc.MODE_CHANNEL, orc.MODE_TOKEN, False)])
+def test_head_shards_reproduce_the_single_gpu_cache(ops, kmode, vmode, shared):
+    """The heads of a cache split in two, as two ranks would hold them, with the compression-time exchanges
+    done by hand (elementwise min / max of the shards' unit extremes, sum of their histograms): scale,
+    min_int, codes and books equal the unsharded run's, every block of a shard's stream equals the unsharded
+    block of the same column, and the attention outputs equal the unsharded ones head by head."""
+    T, B, Hkv, Hq = 512, 2, 4, 8
+    k, v, q = synth(T, B, Hkv, seed=61, Hq=Hq)
+    scaling = 1.0 / math.sqrt(128)
+    full = {}
+    for tag, x, is_k, mode, blk, rel in (("k", k, True, kmode, 64, 0.05), ("v", v, False, vmode, 128, 0.1)):
+        full[tag] = _pipeline(ops, x, is_k, mode, blk, rel, shared)
+    kc = ops.make_cache(*[full["k"][n] for n in ("enc", "bi", "ti", "book", "mi", "sc", "spec", "n", "maxb")])
+    vc = ops.make_cache(*[full["v"][n] for n in ("enc", "bi", "ti", "book", "mi", "sc", "spec", "n", "maxb")])
+    want, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, splits=2)
+    assert ops.read_status(st) == 0
+    halves = [(0, 2), (2, 4)]
+    shard = {}
+    for tag, x, is_k, mode, blk, rel in (("k", k, True, kmode, 64, 0.05), ("v", v, False, vmode, 128, 0.1)):
+        xs = [dev(x[:, :, a:b]) for a, b in halves]
+        spans = mode in (orc.MODE_BLOCK, orc.MODE_TOKEN)
+        hists = [torch.zeros(256, dtype=torch.int64, device="cuda") for _ in halves]
+        if spans:
+            ext = [ops.quant_minmax(xi, mode, blk, shared) for xi in xs]
+            mn = torch.minimum(ext[0][0], ext[1][0]); mx = torch.maximum(ext[0][1], ext[1][1])
+            qs = [ops.quantize_ranged(xi, mode, blk, rel, mn, mx, shared, min_dtype=torch.int16, hist=h) for xi, h in zip(xs, hists)]
+        else:
+            qs = [ops.quantize(xi, mode, blk, rel, shared, min_dtype=torch.int16, hist=h) for xi, h in zip(xs, hists)]
+        book = ops.build_codebook(hists[0] + hists[1])
+        assert torch.equal(book.blob[:32], full[tag]["book"].blob[:32]) and torch.equal(book.blob[64:], full[tag]["book"].blob[64:])
+        f = full[tag]
+        foff, fnum = orc.block_infos(f["bi"].cpu().numpy())
+        fdata = f["enc"][:f["n"]].cpu().numpy()
+        shard[tag] = []
+        for (a, b), (codes, mi, sc, spec, st) in zip(halves, qs):
+            assert ops.read_status(st) == 0
+            assert torch.equal(codes, f["codes"][:, :, a:b])
+            if spans:
+                assert torch.equal(mi, f["mi"]) and torch.equal(sc, f["sc"])
+            Hl = b - a
+            bsz, tsz, _, cap = ops.buffer_sizes(T, B * Hl * 128, is_k)
+            bi = torch.zeros(bsz, dtype=torch.uint8, device="cuda")
+            ti = torch.zeros(tsz // 2, dtype=torch.int16, device="cuda")
+            enc = torch.zeros(cap, dtype=torch.uint8, device="cuda")
+            total, st = ops.encode(codes, is_k, book.encode_table(), bi, ti, enc)
+            assert ops.read_status(st) & ~0x10 == 0
+            n, maxb = (int(t_) for t_ in total.tolist())
+            off, num = orc.block_infos(bi.cpu().numpy())
+            data = enc[:n].cpu().numpy()
+            # block (row r, local column c) of the shard <-> block (r, global column) of the full stream;
+            # V has two blocks (channel halves) per column
+            per = 1 if is_k else 2
+            lc, gc = B * Hl * per, B * Hkv * per
+            for blk_id in range(num.size):
+                r, c = divmod(blk_id, lc)
+                bb, rest = divmod(c, Hl * per)
+                g_id = r * gc + bb * Hkv * per + a * per + rest
+                assert num[blk_id] == fnum[g_id]
+                assert np.array_equal(data[off[blk_id]: off[blk_id] + num[blk_id]], fdata[foff[g_id]: foff[g_id] + fnum[g_id]])
+            shard[tag].append((ops.make_cache(enc, bi, ti, book, mi, sc, spec, n, maxb), (enc, bi, ti, book, mi, sc)))
+    g = Hq // Hkv
+    for i, (a, b) in enumerate(halves):
+        out, st = ops.attn_decode(shard["k"][i][0], shard["v"][i][0], T, B, b - a, dev(q[:, a * g:b * g]), scaling, splits=2)
+        assert ops.read_status(st) == 0
+        assert torch.equal(out, want[:, a * g:b * g])
+
+
 def test_k_matvec(ops):
     rng = np.random.default_rng(0)
     k = rng.standard_normal((192, 1, 8, 128)).astype(np.float16)

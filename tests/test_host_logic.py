@@ -62,6 +62,16 @@ def _gloo_worker(rank, world, port, q):
         ok = torch.equal(out, full)
         ms = sharding.max_over_ranks([1.0 + rank, 5.0 - rank], "cpu")
         bs, bc = sharding.shard_batch(5, world, rank)
+        # the compression-time exchanges of head sharding: unit extremes (min / max) and code histograms (sum)
+        g = torch.Generator().manual_seed(3)
+        x = torch.randn(6, 2, 4, 128, generator=g).half()                 # [T, B, H, D], heads split over the ranks
+        mine = x[:, :, 2 * rank:2 * rank + 2]
+        mn, mx = mine.amin(dim=(2, 3)).reshape(-1), mine.amax(dim=(2, 3)).reshape(-1)
+        sharding.reduce_extremes(mn, mx)
+        ok = ok and torch.equal(mn, x.amin(dim=(2, 3)).reshape(-1)) and torch.equal(mx, x.amax(dim=(2, 3)).reshape(-1))
+        hist = torch.bincount(torch.arange(10 * (rank + 1)) % 7, minlength=256)
+        sharding.reduce_histogram(hist)
+        ok = ok and torch.equal(hist, torch.bincount(torch.arange(10) % 7, minlength=256) + torch.bincount(torch.arange(20) % 7, minlength=256))
         q.put((rank, ok, ms, bs, bc))
     finally:
         dist.destroy_process_group()
