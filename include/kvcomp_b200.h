@@ -96,7 +96,9 @@ typedef struct {
 #define KVC_BOOK_OFF_REFTREE (KVC_BOOK_OFF_ENC + 2048)   /* 512 x 3-byte nodes, reference format */
 #define KVC_BOOK_OFF_TREE   (KVC_BOOK_OFF_REFTREE + 1536) /* 512 x u32 wide nodes */
 #define KVC_BOOK_OFF_LUT    (KVC_BOOK_OFF_TREE + 2048)    /* (1<<KVC_LUT_BITS) x u32 decode-table entries */
-#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUT + 4 * (1 << KVC_LUT_BITS))
+#define KVC_LUTW_BITS       14                            /* the wide table: same entries over a longer window */
+#define KVC_BOOK_OFF_LUTW   (KVC_BOOK_OFF_LUT + 4 * (1 << KVC_LUT_BITS))
+#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUTW + 4 * (1 << KVC_LUTW_BITS))
 
 typedef struct {             /* first 32 bytes of the blob */
     int32_t n_symbols;       /* distinct symbols */
@@ -150,6 +152,14 @@ int kvc_quantize_ranged(const void *x, int64_t T, int64_t B, int64_t H, int64_t 
                         int64_t block, float rel, const void *mn_in, const void *mx_in,
                         uint8_t *codes, void *min_int, int min_bytes, void *scale, unsigned long long *hist,
                         void *workspace, int64_t workspace_bytes, int32_t *status, kvc_stream_t stream);
+
+/* The rotary embedding the cache applies to new keys (models/cache/kvcomp_quant.py:43-48 with
+ * utils/compute.py:25-33: t * cos + rotate_half(t) * sin, each op rounded to fp16) fused with the
+ * transposition into the cache's token-major layout: x device fp16 [B, H, t, D] (as the attention layer
+ * hands it over) -> out device fp16 [t, B, H, D].  cos / sin: device fp16 [B, t, D], or [1, t, D] with
+ * cos_batch_stride = 0.  Same bits as the torch ops. */
+int kvc_rope_store(const void *x, const void *cos_, const void *sin_, void *out, int64_t B, int64_t H, int64_t t,
+                   int64_t D, int64_t cos_batch_stride, kvc_stream_t stream);
 
 /* (codes + min_int) * scale -> fp16 (models/cache/kvcomp_encode.py:146). */
 int kvc_dequant(const uint8_t *codes, const kvc_qmeta *q, int64_t T, int64_t B, int64_t H, int64_t D,
@@ -232,7 +242,9 @@ int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B
  * kernel waits for its staged blocks at most `wait_limit` tries (0 = the default of 2^22); a wait that
  * runs out raises KVC_FLAG_WAIT_TIMEOUT, the CTA stops taking work and the call returns.  starve != 0
  * makes the kernel announce staging bytes that it never copies, so that a test can see a wait run out
- * with nothing in flight; outputs of such a call are undefined.  Process-wide, read at every launch. */
+ * with nothing in flight; outputs of such a call are undefined.  Bit 1 of `starve` keeps the kernel on its
+ * per-CTA 12-bit decode tables where it would otherwise share one 14-bit K table per SM (same results, for
+ * comparing the two forms).  Process-wide, read at every launch. */
 void kvc_attn_debug(int wait_limit, int starve);
 
 /* No counterpart in the reference.  kvc_attn_decode for callers that cannot allocate device memory

@@ -27,7 +27,9 @@ BOOK_OFF_ENC = 64
 BOOK_OFF_REFTREE = BOOK_OFF_ENC + 2048
 BOOK_OFF_TREE = BOOK_OFF_REFTREE + 1536
 BOOK_OFF_LUT = BOOK_OFF_TREE + 2048
-BOOK_BYTES = BOOK_OFF_LUT + 4 * (1 << LUT_BITS)
+LUTW_BITS = 14
+BOOK_OFF_LUTW = BOOK_OFF_LUT + 4 * (1 << LUT_BITS)
+BOOK_BYTES = BOOK_OFF_LUTW + 4 * (1 << LUTW_BITS)
 
 
 class QMeta(C.Structure):
@@ -61,6 +63,7 @@ _SIGNATURES = {
     "kvc_quant_minmax": (_i32, [_vp, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _vp, _vp, _vp, _i64, _vp]),
     "kvc_quantize_ranged": (_i32, [_vp, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _f32, _vp, _vp, _vp, _vp, _i32, _vp,
                                    _vp, _vp, _i64, _vp, _vp]),
+    "kvc_rope_store": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "kvc_dequant": (_i32, [_vp, C.POINTER(QMeta), _i64, _i64, _i64, _i64, _vp, _vp]),
     "kvc_histogram": (_i32, [_vp, _i64, _vp, _vp]),
     "kvc_build_codebook": (_i32, [_vp, _vp, _vp]),

@@ -68,9 +68,13 @@ class KVCompCache(_BASE):
         """Add new tokens (key/value_states: [B, Hkv, t, D]); keys get RoPE here unless pre-RoPE is on."""
         cfg = KVCompCacheConfigStatic.config
         cos, sin = cache_kwargs["cos"], cache_kwargs["sin"]
+        k_rows = None                       # the new keys token-major [t, B, H, D], when one kernel made them so
         if cfg.enable_pre_rope:
             self.coss[layer_idx] = safe_cat(self.coss[layer_idx], cos, dim=1)
             self.sins[layer_idx] = safe_cat(self.sins[layer_idx], sin, dim=1)
+        elif cfg.enable_quant and key_states.is_cuda and key_states.dtype == torch.float16 and key_states.is_contiguous() \
+                and cos.dtype == torch.float16 and key_states.shape[3] % 16 == 0:
+            k_rows = ops.rope_store(key_states, cos, sin)      # rotation and transposition in one pass, torch's bits
         else:
             key_states = apply_rotary_pos_emb_single(key_states, cos, sin)
         if not cfg.enable_quant:
@@ -78,7 +82,7 @@ class KVCompCache(_BASE):
             self.v_plain[layer_idx] = safe_cat(self.v_plain[layer_idx], value_states, dim=2)
             return
         kc, vc = self._ctx(layer_idx, key_states.shape[1])
-        kc.store(key_states.permute(2, 0, 1, 3).contiguous().half())
+        kc.store(k_rows if k_rows is not None else key_states.permute(2, 0, 1, 3).contiguous().half())
         vc.store(value_states.permute(2, 0, 1, 3).contiguous().half())
 
     def update(self, key_states, value_states, layer_idx, cache_kwargs=None):

@@ -540,6 +540,57 @@ extern "C" int kvc_k_matvec(const void *k, const void *q, void *out, int64_t ctx
     return KVC_OK;
 }
 
+// ---- rotary embedding of new keys on their way into the cache -------------------------------------
+// models/cache/kvcomp_quant.py:43-48 rotates the new keys (utils/compute.py:25-33: t * cos + rotate_half(t) * sin,
+// every op a rounded fp16 tensor op) before they enter the recent window; the cache keeps tokens token-major.
+// One pass does both: x [B, H, t, D] -> out [t, B, H, D], same bits as torch's four ops and the transposing copy.
+__global__ void __launch_bounds__(256) rope_store_kernel(const __half *__restrict__ x, const __half *__restrict__ cs,
+                                                         const __half *__restrict__ sn, __half *__restrict__ out,
+                                                         long long B, long long H, long long t, int D, long long cs_bstride) {
+    const int per_row = D / 16;                                  // a thread: 8 channels of the lower half and their partners
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= t * B * H * per_row) return;
+    const int c0 = (int)(i % per_row) * 8, half = D / 2;
+    const long long row = i / per_row, h = row % H, b = (row / H) % B, tok = row / (H * B);
+    const __half *xr = x + ((b * H + h) * t + tok) * D;
+    const __half *cr = cs + b * cs_bstride + tok * D, *sr = sn + b * cs_bstride + tok * D;
+    __half *orow = out + ((tok * B + b) * H + h) * D;
+    const uint4 xa = *reinterpret_cast<const uint4 *>(xr + c0), xb = *reinterpret_cast<const uint4 *>(xr + c0 + half);
+    const uint4 ca = *reinterpret_cast<const uint4 *>(cr + c0), cb = *reinterpret_cast<const uint4 *>(cr + c0 + half);
+    const uint4 sa = *reinterpret_cast<const uint4 *>(sr + c0), sb = *reinterpret_cast<const uint4 *>(sr + c0 + half);
+    const __half *x1 = reinterpret_cast<const __half *>(&xa), *x2 = reinterpret_cast<const __half *>(&xb);
+    const __half *c1 = reinterpret_cast<const __half *>(&ca), *c2 = reinterpret_cast<const __half *>(&cb);
+    const __half *s1 = reinterpret_cast<const __half *>(&sa), *s2 = reinterpret_cast<const __half *>(&sb);
+    uint4 oa, ob;
+    __half *o1 = reinterpret_cast<__half *>(&oa), *o2 = reinterpret_cast<__half *>(&ob);
+    auto mul = [](__half a, __half b2) { return __half2float(__float2half_rn(__fmul_rn(__half2float(a), __half2float(b2)))); };
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        // rotate_half: the lower half meets -x2, the upper half x1
+        o1[k] = __float2half_rn(__fadd_rn(mul(x1[k], c1[k]), mul(__hneg(x2[k]), s1[k])));
+        o2[k] = __float2half_rn(__fadd_rn(mul(x2[k], c2[k]), mul(x1[k], s2[k])));
+    }
+    *reinterpret_cast<uint4 *>(orow + c0) = oa;
+    *reinterpret_cast<uint4 *>(orow + c0 + half) = ob;
+}
+
+extern "C" int kvc_rope_store(const void *x, const void *cos_, const void *sin_, void *out, int64_t B, int64_t H, int64_t t,
+                              int64_t D, int64_t cos_batch_stride, kvc_stream_t stream) {
+    KVC_REQUIRE(x && cos_ && sin_ && out, "kvc_rope_store: null pointer");
+    KVC_REQUIRE(B > 0 && H > 0 && t >= 0 && D > 0 && D % 16 == 0, "kvc_rope_store: bad shape");
+    KVC_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(cos_) | reinterpret_cast<uintptr_t>(sin_) |
+                  reinterpret_cast<uintptr_t>(out)) & 15) == 0, "kvc_rope_store: pointers must be 16-byte aligned");
+    KVC_REQUIRE(cos_batch_stride == 0 || cos_batch_stride == t * D, "kvc_rope_store: cos/sin must be [B, t, D] or [1, t, D]");
+    const long long n = t * B * H * (D / 16);
+    if (n == 0) return KVC_OK;
+    KVC_REQUIRE((n + 255) / 256 < (1ll << 31), "kvc_rope_store: too many elements");
+    rope_store_kernel<<<(unsigned)((n + 255) / 256), 256, 0, kvc_cu(stream)>>>(
+        reinterpret_cast<const __half *>(x), reinterpret_cast<const __half *>(cos_), reinterpret_cast<const __half *>(sin_),
+        reinterpret_cast<__half *>(out), B, H, t, (int)D, cos_batch_stride);
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}
+
 // ---- the quantiser in two calls: extremes first, codes later --------------------------------------
 // For units made of whole (token, sequence) rows -- BlockQuant and TokenQuant, whose units span the heads
 // (models/cache/kvcomp_encode.py:10-13, utils/compute.py:138-143).  When the heads of a cache are split

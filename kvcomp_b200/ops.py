@@ -157,6 +157,22 @@ def quantize_ranged(x, mode, block, rel, mn, mx, batch_shared=True, min_dtype=to
     return codes, min_int, scale, spec, status
 
 
+def rope_store(x, cos, sin, out=None):
+    """New keys x fp16 [B, H, t, D] rotated (t * cos + rotate_half(t) * sin in fp16, as torch evaluates it) and
+    laid out token-major: fp16 [t, B, H, D].  cos / sin: fp16 [B, t, D] or [1, t, D]."""
+    lib = _lib.load()
+    _cuda(x, torch.float16, "key_states")
+    B, H, t, D = x.shape
+    cos, sin = _cuda(cos.contiguous(), torch.float16, "cos"), _cuda(sin.contiguous(), torch.float16, "sin")
+    if cos.shape != sin.shape or cos.dim() != 3 or cos.shape[1:] != (t, D) or cos.shape[0] not in (1, B):
+        raise KvcError("cos / sin must be [B, t, D] or [1, t, D], got %s" % (tuple(cos.shape),))
+    out = torch.empty((t, B, H, D), dtype=torch.float16, device=x.device) if out is None else _cuda(out, torch.float16, "out")
+    with torch.cuda.device(x.device):
+        _lib.check(lib.kvc_rope_store(_p(x), _p(cos), _p(sin), _p(out), B, H, t, D, 0 if cos.shape[0] == 1 and B > 1 else t * D,
+                                      _stream()), "kvc_rope_store")
+    return out
+
+
 def dequant(codes, min_int, scale, spec, out=None):
     lib = _lib.load()
     _cuda(codes, torch.uint8, "codes")
@@ -353,10 +369,11 @@ def attn_decode(kcache, vcache, T, B, Hkv, q, scaling, ktail=None, vtail=None, o
     return out, status
 
 
-def attn_debug(wait_limit=0, starve=False):
-    """Diagnostics of the attention kernel's bounded staging waits (kvc_attn_debug); (0, False) restores
-    the defaults."""
-    _lib.load().kvc_attn_debug(int(wait_limit), int(bool(starve)))
+def attn_debug(wait_limit=0, starve=False, narrow=False):
+    """Diagnostics of the attention kernel (kvc_attn_debug): the bound of its staging waits, the switch that
+    lets a wait run out, and `narrow`, which keeps the kernel on per-CTA 12-bit tables even where one wide
+    table per SM would be used.  No arguments restore the defaults."""
+    _lib.load().kvc_attn_debug(int(wait_limit), int(bool(starve)) | (2 if narrow else 0))
 
 
 def attn_decode_static(kcache, vcache, T, B, Hkv, q, scaling, out, ktail=None, vtail=None, splits=0, status=None):

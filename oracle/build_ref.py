@@ -14,7 +14,9 @@ NAME = "kvc_ref_huffman"
 
 
 def build(ref_root=None, verbose=False):
-    ref_root = ref_root or os.environ.get("REF", "/root/reference")
+    if ref_root is None:
+        from . import ref_root as _rr
+        ref_root = _rr.require()
     ext = os.path.join(ref_root, "kvcomp_cuda_extension")
     if not os.path.isdir(ext):
         raise FileNotFoundError("reference tree not found at %s" % ref_root)
@@ -42,5 +44,7 @@ def load_prebuilt():
 
 
 if __name__ == "__main__":
-    m = build(verbose="-v" in sys.argv)
+    sys.path.insert(0, os.path.dirname(HERE))
+    from oracle import ref_root as _rr
+    m = build(_rr.require(), verbose="-v" in sys.argv)
     print("built", m.__file__)

@@ -18,9 +18,10 @@ NAME = "kvcomp_cuda"
 
 
 def build(ref_root=None, verbose=False):
-    ref_root = ref_root or os.environ.get("REF")
-    if not ref_root:
-        raise RuntimeError("set REF to the root of the reference tree")
+    if ref_root is None:
+        sys.path.insert(0, os.path.dirname(HERE))
+        from oracle import ref_root as _rr
+        ref_root = _rr.require()
     ext = os.path.join(ref_root, "kvcomp_cuda_extension")
     if not os.path.isdir(ext):
         raise FileNotFoundError("reference tree not found at %s" % ref_root)

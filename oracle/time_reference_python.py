@@ -19,9 +19,8 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
-REF = os.environ.get("REF")
-if not REF:
-    raise SystemExit("set REF to the root of the reference tree")
+from oracle import ref_root  # noqa: E402
+REF = ref_root.require()
 sys.path.insert(0, REF)
 
 from utils.compute import QuantMode, quant_ints  # noqa: E402

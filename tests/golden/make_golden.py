@@ -30,8 +30,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("REF", "/root/reference")
 sys.path.insert(0, REPO)
+from oracle import ref_root  # noqa: E402
+REF = ref_root.require()
 sys.path.insert(0, REF)
 
 from utils.compute import (quant, quant_ints, QuantMode, cut_tensor_ctx_len_0, cut_tensor, quant_error,  # noqa: E402

@@ -470,3 +470,19 @@ def test_attend_pre_rope_and_plain(cfg):
         w = torch.softmax(torch.matmul(qd.float(), K.float().repeat_interleave(g, 1).transpose(2, 3)) / math.sqrt(128), dim=-1)
         ref = torch.matmul(w, V.float().repeat_interleave(g, 1))
         assert out.shape == (B, Hq, 1, 128) and (out.float() - ref).abs().max() <= 2e-3 * ref.abs().max()
+
+
+def test_rope_store_equals_torch_ops():
+    """kvc_rope_store against the reference's op sequence (utils/compute.py:25-33) evaluated by torch on
+    CUDA fp16 tensors, followed by the transposition to token-major: the same bits, for batch-wide and
+    broadcast cos / sin."""
+    from kvcomp_b200 import ops
+    from kvcomp_b200.utils.compute import apply_rotary_pos_emb_single
+    g = torch.Generator().manual_seed(2)
+    for B, H, t in ((2, 3, 37), (1, 8, 1), (3, 2, 200)):
+        x = (torch.randn(B, H, t, 128, generator=g) * 3).half().cuda()
+        cos, sin = _rope(t + 11)
+        cos, sin = cos[:, 11:].cuda(), sin[:, 11:].cuda()
+        want = apply_rotary_pos_emb_single(x, cos, sin).permute(2, 0, 1, 3).contiguous()
+        assert torch.equal(ops.rope_store(x, cos, sin), want)
+        assert torch.equal(ops.rope_store(x, cos.expand(B, -1, -1).contiguous(), sin.expand(B, -1, -1).contiguous()), want)
