@@ -96,9 +96,7 @@ typedef struct {
 #define KVC_BOOK_OFF_REFTREE (KVC_BOOK_OFF_ENC + 2048)   /* 512 x 3-byte nodes, reference format */
 #define KVC_BOOK_OFF_TREE   (KVC_BOOK_OFF_REFTREE + 1536) /* 512 x u32 wide nodes */
 #define KVC_BOOK_OFF_LUT    (KVC_BOOK_OFF_TREE + 2048)    /* (1<<KVC_LUT_BITS) x u32 decode-table entries */
-#define KVC_LUTW_BITS       14                            /* the wide table: same entries over a longer window */
-#define KVC_BOOK_OFF_LUTW   (KVC_BOOK_OFF_LUT + 4 * (1 << KVC_LUT_BITS))
-#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUTW + 4 * (1 << KVC_LUTW_BITS))
+#define KVC_BOOK_BYTES      (KVC_BOOK_OFF_LUT + 4 * (1 << KVC_LUT_BITS))
 
 typedef struct {             /* first 32 bytes of the blob */
     int32_t n_symbols;       /* distinct symbols */
@@ -242,9 +240,7 @@ int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B
  * kernel waits for its staged blocks at most `wait_limit` tries (0 = the default of 2^22); a wait that
  * runs out raises KVC_FLAG_WAIT_TIMEOUT, the CTA stops taking work and the call returns.  starve != 0
  * makes the kernel announce staging bytes that it never copies, so that a test can see a wait run out
- * with nothing in flight; outputs of such a call are undefined.  Bit 1 of `starve` keeps the kernel on its
- * per-CTA 12-bit decode tables where it would otherwise share one 14-bit K table per SM (same results, for
- * comparing the two forms).  Process-wide, read at every launch. */
+ * with nothing in flight; outputs of such a call are undefined.  Process-wide, read at every launch. */
 void kvc_attn_debug(int wait_limit, int starve);
 
 /* No counterpart in the reference.  kvc_attn_decode for callers that cannot allocate device memory

@@ -27,9 +27,7 @@ BOOK_OFF_ENC = 64
 BOOK_OFF_REFTREE = BOOK_OFF_ENC + 2048
 BOOK_OFF_TREE = BOOK_OFF_REFTREE + 1536
 BOOK_OFF_LUT = BOOK_OFF_TREE + 2048
-LUTW_BITS = 14
-BOOK_OFF_LUTW = BOOK_OFF_LUT + 4 * (1 << LUT_BITS)
-BOOK_BYTES = BOOK_OFF_LUTW + 4 * (1 << LUTW_BITS)
+BOOK_BYTES = BOOK_OFF_LUT + 4 * (1 << LUT_BITS)
 
 
 class QMeta(C.Structure):

@@ -71,12 +71,6 @@ __device__ __forceinline__ float fix_step(float wmax) { return wmax > 0.f ? wmax
 __device__ __forceinline__ int fix_quant(float w, float step) { return step > 0.f ? __float2int_rn(w / step) : 0; }
 __device__ __forceinline__ float fix_value(float step, int hi, int lo) { return step * fmaf((float)hi, 256.0f, (float)lo); }
 
-// Barrier over one group of 256 threads.  The fused attention kernel runs several independent groups in one
-// CTA (they share the decode tables); group g uses hardware barrier g + 1, a CTA of a single group barrier 0.
-__device__ __forceinline__ void group_sync(int bar) {
-    asm volatile("bar.sync %0, 256;" ::"r"(bar) : "memory");
-}
-
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -105,11 +99,11 @@ __device__ __forceinline__ uint2 pack4_dense(int q0, int q1, int q2, int q3) {
 
 // decode the thread's vector into `row` (its own 33 words), then dot it with the weight words at w:
 // [32 groups of 4 positions][hi | lo][G]
-template <int G, int BITS = KVC_LUT_BITS>
-__device__ __forceinline__ bool decode_rows(const uint8_t *slot, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s, bool esc,
+template <int G>
+__device__ __forceinline__ bool decode_rows(const uint8_t *slot, uint32_t byte_pos, const KvcBookSmem &book, bool esc,
                                             uint32_t *row, const uint32_t *w, int (&hi)[G], int (&lo)[G]) {
     static_assert(G == 2 || G == 4, "two or four query heads");
-    const uint32_t slot_s = kvc_smem_addr(slot);
+    const uint32_t slot_s = kvc_smem_addr(slot), lut_s = kvc_smem_addr(book.lut), tree_s = kvc_smem_addr(book.tree);
     const uint32_t row_s0 = kvc_smem_addr(row);
     // three byte stores per lookup at the position the decoder hands out (its counter starts at the
     // row's address); bytes past the lookup's symbols are rewritten by the next lookup, bytes past
@@ -118,8 +112,8 @@ __device__ __forceinline__ bool decode_rows(const uint8_t *slot, uint32_t byte_p
         asm volatile("st.shared.u8 [%0], %1;\n\tst.shared.u8 [%0+1], %2;\n\tst.shared.u8 [%0+2], %3;"
                      :: "r"(a), "r"(e >> 8), "r"(e >> 16), "r"(e >> 24) : "memory");
     };
-    const bool ok = esc ? kvc_decode_vector<true, 0, decltype(put), false, BITS>(slot_s, byte_pos, lut_s, tree_s, row_s0, put)
-                        : kvc_decode_vector<false, 0, decltype(put), true, BITS>(slot_s, byte_pos, lut_s, tree_s, row_s0, put);
+    const bool ok = esc ? kvc_decode_vector<true, 0>(slot_s, byte_pos, lut_s, tree_s, row_s0, put)
+                        : kvc_decode_vector<false, 0, decltype(put), true>(slot_s, byte_pos, lut_s, tree_s, row_s0, put);
     const uint32_t row_s = kvc_smem_addr(row), w_s = kvc_smem_addr(w);
 #pragma unroll 8
     for (int wg = 0; wg < 32; wg++) {
@@ -147,7 +141,7 @@ template <int G> __device__ __forceinline__ constexpr int w_lo(int c, int g) { r
 
 // decode the thread's vector (staged at shared address slot_s) and dot it with the weight records at
 // shared address w_s (layout: w_hi / w_lo)
-template <int G, bool ESC, int BITS>
+template <int G, bool ESC>
 __device__ __forceinline__ bool decode_dot_impl(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
                                                 uint32_t w_s, int (&hi)[G], int (&lo)[G]) {
     constexpr int SHIFT = G == 1 ? 3 : 4;                      // log2 of the record's bytes
@@ -170,15 +164,16 @@ __device__ __forceinline__ bool decode_dot_impl(uint32_t slot_s, uint32_t byte_p
     };
     // two lookups per round: the weight rows keep WROW - 128 zeroed positions for what is emitted past 127
     static_assert(WROW >= 128 + KVC_DECODE_OVERRUN_PAIR + 1, "weight rows too short for paired lookups");
-    return kvc_decode_vector<ESC, SHIFT, decltype(emit), true, BITS>(slot_s, byte_pos, lut_s, tree_s, w_s >> SHIFT, emit);
+    return kvc_decode_vector<ESC, SHIFT, decltype(emit), true>(slot_s, byte_pos, lut_s, tree_s, w_s >> SHIFT, emit);
 }
 // esc: the book has codes longer than the table window (uniform over the CTA)
-template <int G, int BITS = KVC_LUT_BITS>
-__device__ __forceinline__ bool decode_dot(const uint8_t *slot, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s, bool esc,
+template <int G>
+__device__ __forceinline__ bool decode_dot(const uint8_t *slot, uint32_t byte_pos, const KvcBookSmem &book, bool esc,
                                            const uint32_t *w, int (&hi)[G], int (&lo)[G]) {
-    const uint32_t slot_s = kvc_smem_addr(slot), w_s = kvc_smem_addr(w);
-    return esc ? decode_dot_impl<G, true, BITS>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo)
-               : decode_dot_impl<G, false, BITS>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo);
+    const uint32_t slot_s = kvc_smem_addr(slot), lut_s = kvc_smem_addr(book.lut), tree_s = kvc_smem_addr(book.tree),
+                   w_s = kvc_smem_addr(w);
+    return esc ? decode_dot_impl<G, true>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo)
+               : decode_dot_impl<G, false>(slot_s, byte_pos, lut_s, tree_s, w_s, hi, lo);
 }
 __device__ __forceinline__ bool book_has_long_codes(const void *book) {
     return kvc_book_needs_escape(book);
@@ -245,30 +240,37 @@ __device__ __forceinline__ unsigned short vec_start_bits(const uint16_t *thread_
 // all of them on warps 0-3 when G = 1); lane = 4 consecutive channels.
 // Units that depend on the channel (sc != 0) need tok_div % 64 == 0 so that a block shares them;
 // otherwise scale and min_int are per-token scalars applied after the dot product (k_finish).
-struct KUnit { unsigned short sc[4]; short mi[4]; };     // scale (fp16 bits) and min_int of the lane's 4 channels
+// scale (fp16 bits) and min_int of the lane's 4 consecutive channels, as two vector loads leave them: no
+// arithmetic touches the words before their use, and they occupy 3 or 4 registers instead of 8
+struct KUnit { uint2 sc; uint2 mi; };
+__device__ __forceinline__ unsigned short ku_scale(const KUnit &u, int i) {
+    const uint32_t w = i < 2 ? u.sc.x : u.sc.y;
+    return (unsigned short)((i & 1) ? (w >> 16) : (w & 0xffffu));
+}
+__device__ __forceinline__ int ku_min(const KUnit &u, int i, int min_bytes) {
+    if (min_bytes == 1) return (int)(signed char)((u.mi.x >> (8 * i)) & 0xffu);
+    const uint32_t w = i < 2 ? u.mi.x : u.mi.y;
+    return (int)(short)((i & 1) ? (w >> 16) : (w & 0xffffu));
+}
 
 // global -> registers; issued a tile ahead so that the latency hides behind the decode
 __device__ __forceinline__ void k_units_load(KUnit &u, const kvc_qmeta_dev &m, long long tok0, long long T,
                                              long long b, long long h, int tid) {
     const int lane = tid & 31, sub = (tid >> 5) & 3;
     const long long t = tok0 + sub * 64;
-#pragma unroll
-    for (int i = 0; i < 4; i++) { u.sc[i] = 0x3c00; u.mi[i] = 0; }          // 1.0, 0
-    if (m.sc != 0 && t < T) {
-        const long long ub = kvc_tok_unit(t, m.tok_div) * m.sj + b * m.sb + h * m.sh;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const long long un = ub + (long long)(lane * 4 + i) * m.sc;
-            u.sc[i] = kvc_load_scale_bits(m, un);
-            u.mi[i] = (short)kvc_load_min(m, un);
-        }
+    u.sc = make_uint2(0x3c003c00u, 0x3c003c00u); u.mi = make_uint2(0u, 0u);          // 1.0, 0
+    if (m.sc != 0 && t < T) {                              // channel units lie side by side (sc == 1, checked by the host)
+        const long long un = kvc_tok_unit(t, m.tok_div) * m.sj + b * m.sb + h * m.sh + lane * 4;
+        u.sc = *reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(m.scale) + un);
+        if (m.min_bytes == 1) u.mi.x = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const int8_t *>(m.min_int) + un);
+        else u.mi = *reinterpret_cast<const uint2 *>(reinterpret_cast<const int16_t *>(m.min_int) + un);
     }
 }
 
 // ROWS: the layout of decode_rows (grouped queries in the attention kernel) instead of w_hi / w_lo
 template <int G, bool ROWS = false>
 __device__ __forceinline__ void k_weights_build(uint32_t *w, float *step, float *zp, const float *qf, const KUnit &u,
-                                                bool channel_units, long long tok0, long long T, int tid) {
+                                                bool channel_units, int min_bytes, long long tok0, long long T, int tid) {
     const int lane = tid & 31, wp = tid >> 5, sub = wp & 3;
     constexpr int GH = G >= 2 ? G / 2 : 1;
     if (G == 1 && wp >= 4) return;
@@ -280,9 +282,9 @@ __device__ __forceinline__ void k_weights_build(uint32_t *w, float *step, float 
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const float q = live ? qf[g * 128 + lane * 4 + i] : 0.f;
-            const float sc = kvc_scale_value(u.sc[i]);
+            const float sc = kvc_scale_value(ku_scale(u, i));
             wv[i] = q * sc;
-            z = fmaf((float)u.mi[i] * sc, q, z);
+            z = fmaf((float)ku_min(u, i, min_bytes) * sc, q, z);
         }
         float mx = fmaxf(fmaxf(fabsf(wv[0]), fabsf(wv[1])), fmaxf(fabsf(wv[2]), fabsf(wv[3])));
         mx = kvc_warp_max(mx);
@@ -317,7 +319,7 @@ __device__ __forceinline__ void k_weights(uint32_t *w, float *step, float *zp, c
                                           long long tok0, long long T, long long b, long long h, int tid) {
     KUnit u;
     k_units_load(u, m, tok0, T, b, h, tid);
-    k_weights_build<G>(w, step, zp, qf, u, m.sc != 0, tok0, T, tid);
+    k_weights_build<G>(w, step, zp, qf, u, m.sc != 0, m.min_bytes, tok0, T, tid);
 }
 
 template <int G>
@@ -372,12 +374,12 @@ __device__ __forceinline__ void k_finish(float (&s)[G], const int (&hi)[G], cons
 // barriers (two with ROWS).
 template <int G, bool ROWS = false>
 __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red, int16_t *q16, const float (&wv)[G],
-                                          int tid, int bar = 0) {
+                                          int tid) {
     const int lane = tid & 31, warp = tid >> 5, grp = tid >> 7, tl = tid & 127;
 #pragma unroll
     for (int g = 0; g < G; g++) { float mx = kvc_warp_max(fabsf(wv[g])); if (lane == 0) red[warp * G + g] = mx; }
     if (!ROWS && tl < 4) for (int g = 0; g < G; g++) q16[(grp * G + g) * 132 + 128 + tl] = 0;
-    group_sync(bar);
+    __syncthreads();
     if (ROWS) {
         // four consecutive tokens make one weight word per head: their 16-bit values reach the first of
         // the four lanes by shuffles, no scratch and no barrier in between
@@ -396,7 +398,7 @@ __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red
                 row[((tl >> 2) * 2 + 0) * G + g] = r.x; row[((tl >> 2) * 2 + 1) * G + g] = r.y;
             }
         }
-        group_sync(bar);
+        __syncthreads();
         return;
     }
 #pragma unroll
@@ -407,7 +409,7 @@ __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red
         q16[(grp * G + g) * 132 + tl] = (int16_t)fix_quant(wv[g], st);
         if (tl == 0) vstep[grp * G + g] = st;
     }
-    group_sync(bar);
+    __syncthreads();
 #pragma unroll
     for (int g = 0; g < G; g++) {
         const int16_t *qq = q16 + (grp * G + g) * 132 + tl;
@@ -416,7 +418,7 @@ __device__ __forceinline__ void v_weights(uint32_t *ps, float *vstep, float *red
         row[w_hi<G>(tl, g)] = r.x; row[w_lo<G>(tl, g)] = r.y;
         if (tl < WROW - 128) { row[w_hi<G>(128 + tl, g)] = 0u; row[w_lo<G>(128 + tl, g)] = 0u; }
     }
-    group_sync(bar);
+    __syncthreads();
 }
 
 // ---- fused K: raw scores ------------------------------------------------------------------------
@@ -460,7 +462,7 @@ __global__ void __launch_bounds__(NTHR) fused_qk_kernel(CacheDev kc, long long T
     for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
     const uint32_t start = vec_start(kc.thread_info, blk, v);
     bool ok = sm.ok[sub] && start < sm.nb[sub];                // a vector begins inside its block
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + start, kvc_smem_addr(sm.book.lut), kvc_smem_addr(sm.book.tree), esc, sm.w + sub * 2 * WROW * G, hi, lo);
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + start, sm.book, esc, sm.w + sub * 2 * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
     float s[G];
     k_finish<G>(s, hi, lo, sm.step + sub * G, sm.zp + sub * G, sm.qsum, kc.q.sc != 0, kvc_scale_value(ksc), (float)kmi);
@@ -526,7 +528,7 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
     for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
     const uint32_t start = vec_start(vc.thread_info, blk, v);
     bool ok = sm.ok[sub] && start < sm.nb[sub];
-    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + start, kvc_smem_addr(sm.book.lut), kvc_smem_addr(sm.book.tree), esc, sm.ps + grp * 2 * WROW * G, hi, lo);
+    if (ok) ok = decode_dot<G>(sm.slot[sub], sm.lead[sub] + start, sm.book, esc, sm.ps + grp * 2 * WROW * G, hi, lo);
     if (!ok) atomicOr(status, KVC_FLAG_BAD_STREAM);
 #pragma unroll
     for (int g = 0; g < G; g++) {
@@ -538,7 +540,8 @@ __global__ void __launch_bounds__(NTHR) fused_pv_kernel(CacheDev vc, long long T
 
 // ---- one-pass decode attention -------------------------------------------------------------------
 template <int G>
-struct alignas(32) AttnSmem {                     // the state of one group of 256 threads
+struct alignas(32) AttnSmem {                     // followed in shared memory by 4 K slots, 4 V slots (sized at launch),
+    KvcBookSmem bookK, bookV;         // SLOT_PAD bytes that a corrupt stream's decoder overrun may read
     alignas(32) uint32_t w[4 * VecWords<G, (G >= 2)>::value];     // K weight words; reused by v_weights (scratch), the tail and the final cross-group sum
     alignas(32) uint32_t ps[2 * VecWords<G, (G >= 2)>::value];    // V weight words
     float kstep[4 * G], zp[4 * G];
@@ -551,7 +554,6 @@ struct alignas(32) AttnSmem {                     // the state of one group of 2
     uint32_t nbK[4], nbV[4];          // byte counts of the staged blocks
     int okK[4], okV[4];
     int next_j;                       // item the CTA drew for after the current one
-    int dead;                         // a staging wait ran out: the CTA takes no further tiles
 };
 
 struct AttnParams {
@@ -573,61 +575,35 @@ struct AttnParams {
     int starve;                   // tests of the bounded waits only: announce bytes that are never copied
 };
 
-// The decode tables of the K and V books, one copy per CTA: wide-tree nodes and the table over KBITS / 12 bits.
-template <int KBITS>
-struct alignas(16) AttnBooks {
-    uint32_t treeK[512];
-    uint32_t lutK[1 << KBITS];
-    uint32_t treeV[512];
-    uint32_t lutV[KVC_LUT_SIZE];
-};
-// bytes of a group's staging area: 4 K slots, 4 V slots, padding a corrupt stream's decoder overrun may read,
-// and (grouped queries) a row of decoded symbols per thread
-template <int G>
-__host__ __device__ inline size_t attn_group_area(uint32_t slotK, uint32_t slotV) {
-    return 4 * (size_t)(slotK + slotV) + SLOT_PAD + (G >= 2 ? NTHR * ROW_STRIDE : 0);
-}
-
-// One CTA = NG independent groups of 256 threads that share the decode tables.  NG = 1: several CTAs per SM,
-// each with its own copy of the 12-bit tables.  NG = 3 (one CTA per SM): one copy, which leaves room for the
-// K book's table over KBITS = 14 bits -- more symbols per lookup at 4 to 6 bits per symbol.
 // BULK: stage with bulk asynchronous copies (one tile phase ahead) instead of plain loads.
-template <int G, bool BULK, int NG, int KBITS>
-__global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn_decode_kernel(AttnParams p) {
+template <int G, bool BULK>
+__global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    const int gid = NG > 1 ? (int)threadIdx.x / NTHR : 0;      // the thread's group, and its barrier
-    const int bar = NG > 1 ? gid + 1 : 0;
-    AttnBooks<KBITS> &books = *reinterpret_cast<AttnBooks<KBITS> *>(smem_raw);
-    AttnSmem<G> &sm = reinterpret_cast<AttnSmem<G> *>(smem_raw + sizeof(AttnBooks<KBITS>))[gid];
-    uint8_t *const slotsK = smem_raw + sizeof(AttnBooks<KBITS>) + NG * sizeof(AttnSmem<G>) + gid * attn_group_area<G>(p.slotK_bytes, p.slotV_bytes);
-    uint8_t *const slotsV = slotsK + 4 * p.slotK_bytes;
+    AttnSmem<G> &sm = *reinterpret_cast<AttnSmem<G> *>(smem_raw);
+    uint8_t *const slotsK = smem_raw + sizeof(AttnSmem<G>), *const slotsV = slotsK + 4 * p.slotK_bytes;
     constexpr bool ROWS = G >= 2;                          // grouped queries: decode into rows, multiply afterwards
-    const int tid = NG > 1 ? (int)threadIdx.x % NTHR : (int)threadIdx.x;      // index inside the group
-    uint32_t *const myrow = reinterpret_cast<uint32_t *>(slotsV + 4 * p.slotV_bytes + SLOT_PAD) + tid * (ROW_STRIDE / 4);
-    const int lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
+    uint32_t *const myrow = reinterpret_cast<uint32_t *>(slotsV + 4 * p.slotV_bytes + SLOT_PAD) + threadIdx.x * (ROW_STRIDE / 4);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
     const int grp = tid >> 7, ch = tid & 127;
-    const uint32_t lutK_s = kvc_smem_addr(books.lutK), treeK_s = kvc_smem_addr(books.treeK);
-    const uint32_t lutV_s = kvc_smem_addr(books.lutV), treeV_s = kvc_smem_addr(books.treeV);
     // launched with programmatic stream serialisation: nothing in memory is touched before the kernel
     // ahead of this one in the stream has completed
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const long long T = p.T, B = p.B, Hkv = p.Hkv, Hq = p.Hq;
-    const long long cols = B * Hkv, Gt = Hq / Hkv;
+    // shapes fit 32 bits (the host checks): 64-bit arithmetic only where block ids and addresses are formed
+    const int T = (int)p.T, B = (int)p.B, Hkv = (int)p.Hkv, Hq = (int)p.Hq;
+    const int cols = B * Hkv, Gt = Hq / Hkv;
     const int n_tiles = p.n_tiles;
     const kvc_qmeta_dev &km = p.k.q, &vm = p.v.q;
     int flags = 0;
 
     // The work is cut into items: a column (one sequence, one KV head) x one of `splits` runs of
-    // `tiles_per_split` tiles; item j = column * splits + run.  A group is a worker; there are P of them.
-    // Without a scheduling counter worker i takes the items [work*i/P, work*(i+1)/P).  With one it takes
-    // items i and P + i and draws every further item from the counter, two items ahead of its use so that
-    // the answer has an item's time to arrive: workers that run faster (the warp schedulers favour some of
-    // an SM's warps) take more.
+    // `tiles_per_split` tiles; item j = column * splits + run.  Without a scheduling counter CTA i of P
+    // takes the items [work*i/P, work*(i+1)/P).  With one it takes items i and P + i and draws every
+    // further item from the counter, two items ahead of its use so that the answer has an item's time
+    // to arrive: CTAs that run faster (the warp schedulers favour some of an SM's CTAs) take more.
     struct Item { int col, t_lo, t_hi, part; };            // part: the run's index within its column
     const bool draw = p.sched != nullptr;
-    const int P = (int)gridDim.x * NG;                      // items are counted in 32 bits (the host checks the range)
-    const int me = gid * (int)gridDim.x + (int)blockIdx.x;  // the groups of one SM start far apart in the item order
-    const int w_hi = draw ? (int)p.work : (int)(p.work * (me + 1) / P);
+    const int P = (int)gridDim.x;                           // items are counted in 32 bits (the host checks the range)
+    const int w_hi = draw ? (int)p.work : (int)(p.work * (blockIdx.x + 1) / P);
     auto item_of = [&](int j, Item &it) -> bool {
         if (j >= w_hi) return false;
         const int n_long = (int)cols * p.long_runs;          // items of long runs; the short runs follow: the last
@@ -649,34 +625,25 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
     auto validV = [&](bool on, int tile, int l) { return on && (long long)tile * 256 + (l >> 1) * 128 < T; };
 
     Item it, nit;
-    int j_it = draw ? me : (int)(p.work * me / P), j_n1 = draw ? P + me : j_it + 1;
+    int j_it = draw ? (int)blockIdx.x : (int)(p.work * blockIdx.x / P), j_n1 = draw ? P + (int)blockIdx.x : j_it + 1;
     bool have = item_of(j_it, it), have_next = have && item_of(j_n1, nit);
     int drawn = 0;                                         // thread 0: the counter's answer, used an item later
     const bool any_tiles = have && it.t_lo < it.t_hi;      // items are empty only when the cache has no compressed part
 
     if (BULK) {
-        if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); sm.dead = 0; }
-        group_sync(bar);
+        if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); }
+        __syncthreads();
         if (warp == 0 && any_tiles) {
             stage_bulk(p.k, validK(true, it.t_lo, lane & 3), blkK_of(it.col, it.t_lo, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, sm.nbK, &sm.bar[0], lane, p.starve != 0);
             stage_bulk(p.v, validV(true, it.t_lo, lane & 3), blkV_of(it.col, it.t_lo, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, sm.nbV, &sm.bar[1], lane, p.starve != 0);
         }
-    } else if (tid == 0) sm.dead = 0;
+    }
     bool escK = false, escV = false;
     if (p.T > 0) {                                         // (no streams at all while nothing is compressed yet)
-        // the whole CTA copies the tables: tree and 12-bit table lie back to back in a book, the wide table behind
-        const uint8_t *bk = reinterpret_cast<const uint8_t *>(p.k.book), *bv = reinterpret_cast<const uint8_t *>(p.v.book);
-        const int t_all = (int)threadIdx.x, n_all = NTHR * NG;
-        auto copy16 = [&](void *dst, const uint8_t *src, int bytes) {
-            for (int i = t_all; i < bytes / 16; i += n_all) reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
-        };
-        copy16(books.treeK, bk + KVC_BOOK_OFF_TREE, 2048);
-        copy16(books.lutK, bk + (KBITS == KVC_LUT_BITS ? KVC_BOOK_OFF_LUT : KVC_BOOK_OFF_LUTW), 4 << KBITS);
-        copy16(books.treeV, bv + KVC_BOOK_OFF_TREE, 2048);
-        copy16(books.lutV, bv + KVC_BOOK_OFF_LUT, 4 * KVC_LUT_SIZE);
+        kvc_load_book(sm.bookK, p.k.book, tid, NTHR);
+        kvc_load_book(sm.bookV, p.v.book, tid, NTHR);
         escK = book_has_long_codes(p.k.book); escV = book_has_long_codes(p.v.book);
     }
-    if (NG > 1) __syncthreads();                           // the only CTA-wide barrier: the tables are in place
 
     // Per-thread metadata of a tile (vector start offsets, the token's V scale / min_int, the K unit
     // parameters of the warp's block) is fetched one tile ahead, so that no global-memory latency
@@ -728,14 +695,15 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
     const long long hq0 = h * Gt + p.g0;
     if (draw && tid == 0) drawn = atomicAdd(&p.sched[0], 1);
     q_store();                                             // fetched during the previous item's last tile
-    group_sync(bar);
+    __syncthreads();
     q_sums<G>(sm.qf, sm.qsum, tid);
-    group_sync(bar);                                       // books, q and (unbuffered) slots are in place
+    __syncthreads();                                       // books, q and (unbuffered) slots are in place
     float m_run[G], l_run[G], acc[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
 
-    for (int tile = it.t_lo; tile < it.t_hi; tile++) {
+    int tile = it.t_lo;
+    for (; tile < it.t_hi; tile++) {
         const long long tok0 = (long long)tile * 256, t = tok0 + tid;
         const long long blkK = (tok0 / 64 + sub) * cols + col;
         const long long gI = tok0 / 128 + grp;
@@ -747,36 +715,31 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
             n_on = have_next && nit.t_lo < nit.t_hi; n_col = n_on ? nit.col : col; n_tile = n_on ? nit.t_lo : 0;
             if (have_next) q_fetch(nit.col);
         }
-        load_meta(n_on, n_col, n_tile, nxt);
         if (!BULK) {
             if (actK) { uint32_t ld, nb; bool ok = stage(p.k, blkK, slotsK + sub * p.slotK_bytes, &ld, &nb, v); if (v == 0) { sm.leadK[sub] = ld; sm.nbK[sub] = nb; sm.okK[sub] = ok; } }
             if (actV) { uint32_t ld, nb; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, &nb, v); if (v == 0) { sm.leadV[sub] = ld; sm.nbV[sub] = nb; sm.okV[sub] = ok; } }
         }
-        k_weights_build<G, ROWS>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, tok0, T, tid);
-        // A wait that runs out: the tile is not decoded, the CTA issues no further copies and takes no
-        // further tiles (what it had in flight is waited for once more, bounded, before it returns).
+        k_weights_build<G, ROWS>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, km.min_bytes, tok0, T, tid);
+        // A wait that runs out: the thread does not decode, and at the phase's closing barrier (which also joins
+        // the threads' verdicts) the CTA stops before it arms the barrier that never completed again: it issues
+        // no further copies and takes no further tiles; what it had in flight is waited for once more,
+        // bounded, before it returns.
+        bool k_landed = true;
         if (BULK) {
-            if (kvc_mbar_wait(&sm.bar[0], par & 1u, p.wait_limit)) par ^= 1u;
-            else { flags |= KVC_FLAG_WAIT_TIMEOUT; sm.dead = 1; }
+            k_landed = kvc_mbar_wait(&sm.bar[0], par & 1u, p.wait_limit);
+            if (k_landed) par ^= 1u; else flags |= KVC_FLAG_WAIT_TIMEOUT;
         }
-        group_sync(bar);
-#ifndef KVC_EXP_NODEAD
-        if (BULK && sm.dead != 0) break;
-#endif
+        __syncthreads();
         // ---- K: scores of this tile's tokens
         float s[G];
         if (actK) {
             int hi[G], lo[G];
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
-#ifndef KVC_EXP_NONB
-            bool ok = sm.okK[sub] && (uint32_t)(cur.startK >> 3) < sm.nbK[sub];      // a vector begins inside its block
-#else
-            bool ok = sm.okK[sub];
-#endif
+            bool ok = k_landed && sm.okK[sub] && (uint32_t)(cur.startK >> 3) < sm.nbK[sub];      // a vector begins inside its block
             if (ok) {
-                if constexpr (ROWS) ok = decode_rows<G, KBITS>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), lutK_s, treeK_s, escK, myrow, sm.w + sub * VecWords<G, true>::value, hi, lo);
-                else ok = decode_dot<G, KBITS>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), lutK_s, treeK_s, escK, sm.w + sub * VecWords<G, false>::value, hi, lo);
+                if constexpr (ROWS) ok = decode_rows<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, myrow, sm.w + sub * VecWords<G, true>::value, hi, lo);
+                else ok = decode_dot<G>(slotsK + sub * p.slotK_bytes, sm.leadK[sub] + (cur.startK >> 3), sm.bookK, escK, sm.w + sub * VecWords<G, false>::value, hi, lo);
             }
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
             k_finish<G>(s, hi, lo, sm.kstep + sub * G, sm.zp + sub * G, sm.qsum, km.sc != 0, kvc_scale_value(cur.ksc), (float)cur.kmi);
@@ -787,7 +750,12 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
         // ---- online softmax over the tile
 #pragma unroll
         for (int g = 0; g < G; g++) { float mx = kvc_warp_max(s[g]); if (lane == 0) sm.red[0][warp * G + g] = mx; }
-        group_sync(bar);                                   // also: every thread is done with the K slots
+        // every thread is done with the K slots (and: did any thread's K wait run out?)
+        if (BULK) { if (__syncthreads_or(flags & KVC_FLAG_WAIT_TIMEOUT)) break; }
+        else __syncthreads();
+        // the next tile's per-thread metadata is asked for now and first touched when that tile begins: it is in
+        // flight during the V phase only, and the K decode above ran without its registers
+        load_meta(n_on, n_col, n_tile, nxt);
         if (BULK && warp == 0)                             // next tile's K blocks land during the V phase
             stage_bulk(p.k, validK(n_on, n_tile, lane & 3), blkK_of(n_col, n_tile, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, sm.nbK, &sm.bar[0], lane, p.starve != 0);
         float alpha[G], wv[G];
@@ -805,7 +773,7 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
             if (lane == 0) { sm.red[1][warp * G + g] = ssum; sm.red[2][warp * G + g] = zsum; }
         }
         // (the K weights are spent: their memory is the scratch of the V weights' 16-bit values)
-        v_weights<G, ROWS>(sm.ps, sm.vstep, sm.red[3], reinterpret_cast<int16_t *>(sm.w), wv, tid, bar);      // three barriers inside
+        v_weights<G, ROWS>(sm.ps, sm.vstep, sm.red[3], reinterpret_cast<int16_t *>(sm.w), wv, tid);      // three barriers inside
 #pragma unroll
         for (int g = 0; g < G; g++) {
             float lt = 0.f;
@@ -815,7 +783,7 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
         }
         const bool v_landed = !BULK || kvc_mbar_wait(&sm.bar[1], par >> 1, p.wait_limit);
         if (BULK && v_landed) par ^= 2u;
-        if (!v_landed) { flags |= KVC_FLAG_WAIT_TIMEOUT; sm.dead = 1; }     // seen by all at the tile's last barrier
+        if (!v_landed) flags |= KVC_FLAG_WAIT_TIMEOUT;
         // ---- V: accumulate this tile's contribution for the thread's (group, channel)
         float dv[G];
 #pragma unroll
@@ -824,14 +792,10 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
             int hi[G], lo[G];
 #pragma unroll
             for (int g = 0; g < G; g++) { hi[g] = 0; lo[g] = 0; }
-#ifndef KVC_EXP_NONB
             bool ok = v_landed && sm.okV[sub] && (uint32_t)(cur.startV >> 3) < sm.nbV[sub];
-#else
-            bool ok = v_landed && sm.okV[sub];
-#endif
             if (ok) {
-                if constexpr (ROWS) ok = decode_rows<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), lutV_s, treeV_s, escV, myrow, sm.ps + grp * VecWords<G, true>::value, hi, lo);
-                else ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), lutV_s, treeV_s, escV, sm.ps + grp * VecWords<G, false>::value, hi, lo);
+                if constexpr (ROWS) ok = decode_rows<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, myrow, sm.ps + grp * VecWords<G, true>::value, hi, lo);
+                else ok = decode_dot<G>(slotsV + sub * p.slotV_bytes, sm.leadV[sub] + (cur.startV >> 3), sm.bookV, escV, sm.ps + grp * VecWords<G, false>::value, hi, lo);
             }
             if (!ok) flags |= KVC_FLAG_BAD_STREAM;
 #pragma unroll
@@ -842,17 +806,14 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
         }
 #pragma unroll
         for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
-        group_sync(bar);                                   // every thread is done with the V slots, weights and sums
-#ifndef KVC_EXP_NODEAD
-        if (BULK && sm.dead != 0) break;                   // (the K copy issued above is waited for at the end)
-#endif
+        // every thread is done with the V slots, weights and sums; did any thread's wait run out?
+        if (BULK) { if (__syncthreads_or(flags & KVC_FLAG_WAIT_TIMEOUT)) break; }   // (the K copy issued above is waited for at the end)
+        else __syncthreads();
         if (BULK && warp == 0)                             // next tile's V blocks land during its K phase
             stage_bulk(p.v, validV(n_on, n_tile, lane & 3), blkV_of(n_col, n_tile, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, sm.nbV, &sm.bar[1], lane, p.starve != 0);
         cur = nxt;
     }
-#ifndef KVC_EXP_NODEAD
-    if (BULK && sm.dead != 0) break;                       // no partial result is written: the status word says why
-#endif
+    if (BULK && tile < it.t_hi) break;                     // a wait ran out: no partial result is written, the status word says why
 
     // ---- uncompressed tail (the recent window), handled with the column's last tiles: dense fp16 rows
     if (p.Tr > 0 && it.t_hi == n_tiles) {
@@ -860,7 +821,7 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
         for (long long r0 = 0; r0 < p.Tr; r0 += 256) {
             const long long r = r0 + tid;
             const bool act = r < p.Tr;
-            group_sync(bar);
+            __syncthreads();
             float s[G];
 #pragma unroll
             for (int g = 0; g < G; g++) s[g] = act ? 0.f : -CUDART_INF_F;
@@ -879,7 +840,7 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
             }
 #pragma unroll
             for (int g = 0; g < G; g++) { float mx = kvc_warp_max(s[g]); if (lane == 0) sm.red[0][warp * G + g] = mx; }
-            group_sync(bar);
+            __syncthreads();
             float alpha[G];
 #pragma unroll
             for (int g = 0; g < G; g++) {
@@ -894,7 +855,7 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
                 const float ssum = kvc_warp_sum(pr);
                 if (lane == 0) sm.red[1][warp * G + g] = ssum;
             }
-            group_sync(bar);
+            __syncthreads();
             float dv[G];
 #pragma unroll
             for (int g = 0; g < G; g++) {
@@ -920,11 +881,11 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
     const long long head0 = b * Hq + hq0;
     if (p.splits == 1) {
         // ---- the item is the whole column: combine the CTA's two token groups and write the output
-        group_sync(bar);
+        __syncthreads();
         float *sumbuf = reinterpret_cast<float *>(sm.w);       // [2][128][G]
 #pragma unroll
         for (int g = 0; g < G; g++) sumbuf[(grp * 128 + ch) * G + g] = acc[g];
-        group_sync(bar);
+        __syncthreads();
         if (tid < 128) {
 #pragma unroll
             for (int g = 0; g < G; g++)
@@ -940,7 +901,7 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
         }
     }
     if (draw && tid == 0) sm.next_j = drawn;
-    group_sync(bar);                                       // the sums are read before the next column's weights overwrite them
+    __syncthreads();                                       // the sums are read before the next column's weights overwrite them
     const int j_n2 = draw ? 2 * P + sm.next_j : j_n1 + 1;
     it = nit; have = have_next; j_it = j_n1; j_n1 = j_n2;
     have_next = have && item_of(j_n1, nit);
@@ -951,9 +912,9 @@ __global__ void __launch_bounds__(NTHR * NG, NG > 1 ? 1 : (G == 4 ? 2 : 3)) attn
         if (!kvc_mbar_wait(&sm.bar[1], par >> 1, p.wait_limit)) flags |= KVC_FLAG_WAIT_TIMEOUT;
     }
     if (flags) atomicOr(p.status, flags);
-    if (draw && tid == 0) {               // the last worker to finish leaves the scheduling counters zeroed for the next launch
+    if (draw && tid == 0) {               // the last CTA to finish leaves the scheduling counters zeroed for the next launch
         __threadfence();
-        if (atomicAdd(&p.sched[1], 1) == P - 1) { p.sched[0] = 0; p.sched[1] = 0; __threadfence(); }
+        if (atomicAdd(&p.sched[1], 1) == (int)gridDim.x - 1) { p.sched[0] = 0; p.sched[1] = 0; __threadfence(); }
     }
 }
 
@@ -1007,8 +968,15 @@ int check_cache(const kvc_cache *c, const char *who, bool is_k) {
     KVC_REQUIRE(c->q.tok_div > 0, "%s: tok_div must be positive", who);
     KVC_REQUIRE((reinterpret_cast<uintptr_t>(c->book) & 15) == 0 && (reinterpret_cast<uintptr_t>(c->block_info) & 7) == 0,
                 "%s: book must be 16-byte and block_info 8-byte aligned", who);
-    if (is_k) KVC_REQUIRE(c->q.sc == 0 || c->q.tok_div % 64 == 0,
-                          "%s: K units that depend on the channel must cover whole 64-token blocks", who);
+    if (is_k) {
+        KVC_REQUIRE(c->q.sc == 0 || c->q.tok_div % 64 == 0,
+                    "%s: K units that depend on the channel must cover whole 64-token blocks", who);
+        // the kernels fetch the units of 4 neighbouring channels with one load
+        KVC_REQUIRE(c->q.sc == 0 || (c->q.sc == 1 && c->q.sj % 4 == 0 && c->q.sb % 4 == 0 && c->q.sh % 4 == 0 &&
+                                     (reinterpret_cast<uintptr_t>(c->q.scale) & 7) == 0 &&
+                                     (reinterpret_cast<uintptr_t>(c->q.min_int) & (c->q.min_bytes == 1 ? 3 : 7)) == 0),
+                    "%s: per-channel K units must be contiguous over the channels and 8-byte aligned", who);
+    }
     else KVC_REQUIRE(c->q.sc == 0, "%s: V units that depend on the channel are not supported by the fused kernels", who);
     return KVC_OK;
 }
@@ -1071,8 +1039,8 @@ extern "C" int kvc_fused_pv(const kvc_cache *v, int64_t T, int64_t B, int64_t Hk
 }
 
 // Diagnostics for tests of the bounded waits (kvc_attn_debug): process-wide, read at every launch.
-static int g_wait_limit = 0, g_starve = 0, g_narrow = 0;
-extern "C" void kvc_attn_debug(int wait_limit, int starve) { g_wait_limit = wait_limit; g_starve = starve & 1; g_narrow = (starve >> 1) & 1; }
+static int g_wait_limit = 0, g_starve = 0;
+extern "C" void kvc_attn_debug(int wait_limit, int starve) { g_wait_limit = wait_limit; g_starve = starve; }
 
 // CTAs per SM the attention kernel is launched with at most (its launch bounds ask for this many)
 constexpr int ATTN_CTAS_PER_SM = 3;
@@ -1136,7 +1104,7 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     KVC_REQUIRE(T + Tr > 0, "kvc_attn_decode: empty cache");
     KVC_REQUIRE(Tr == 0 || ((reinterpret_cast<uintptr_t>(ktail) & 15) == 0), "kvc_attn_decode: ktail must be 16-byte aligned");
     const long long n_tiles = (T + 255) / 256, cols = B * Hkv;
-    KVC_REQUIRE(n_tiles < (1ll << 30) && cols < (1ll << 30), "kvc_attn_decode: shape too large");
+    KVC_REQUIRE(T < (1ll << 31) - 1024 && cols < (1ll << 30) && B * Hq < (1ll << 30), "kvc_attn_decode: shape too large");
     // every column is cut into runs of tiles; each (column, run) is one item of work.  splits > 0: that many
     // equal runs.  Otherwise long runs and, at the end of each column, short ones (plan_runs).
     int tps, long_runs, short_tiles;
@@ -1176,9 +1144,7 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     // decoder's two words of read-ahead
     p.slotK_bytes = ((p.k.max_block + 15u + 15u) & ~15u) + 16u;
     p.slotV_bytes = ((p.v.max_block + 15u + 15u) & ~15u) + 16u;
-    int smem_optin = 0, devid = 0;
-    KVC_CUDA_OK(cudaGetDevice(&devid));
-    KVC_CUDA_OK(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, devid));
+    const size_t slot_total = 4 * (size_t)(p.slotK_bytes + p.slotV_bytes) + SLOT_PAD;
     // bulk copies widen every block to 16-byte boundaries: both streams must start on one
     const bool bulk = T > 0 && (reinterpret_cast<uintptr_t>(k->encoded) & 15) == 0 && (reinterpret_cast<uintptr_t>(v->encoded) & 15) == 0;
     const int sms = kvc_sm_count();
@@ -1186,29 +1152,19 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     for (long long g0 = 0; g0 < Gt;) {
         const int G = next_chunk(Gt - g0);
         p.g0 = g0;
-#define KVC_AT(GG, BB, NGG, KB)                                                                                 \
+#define KVC_AT(GG, BB)                                                                                          \
     {                                                                                                           \
-        const size_t smem = sizeof(AttnBooks<KB>) + (NGG) * (sizeof(AttnSmem<GG>) + attn_group_area<GG>(p.slotK_bytes, p.slotV_bytes)); \
-        if (int rc = set_smem(attn_decode_kernel<GG, BB, NGG, KB>, smem)) return rc;                            \
+        const size_t smem = slot_total + sizeof(AttnSmem<GG>) + ((GG) >= 2 ? NTHR * ROW_STRIDE : 0);               \
+        if (int rc = set_smem(attn_decode_kernel<GG, BB>, smem)) return rc;                                     \
         int occ = 0;                                                                                            \
-        KVC_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, attn_decode_kernel<GG, BB, NGG, KB>, NTHR * (NGG), smem)); \
+        KVC_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, attn_decode_kernel<GG, BB>, NTHR, smem)); \
         KVC_REQUIRE(occ >= 1, "kvc_attn_decode: %zu bytes of shared memory do not fit an SM", smem);             \
-        const int per_sm = (NGG) > 1 ? 1 : (occ < ATTN_CTAS_PER_SM ? occ : ATTN_CTAS_PER_SM);                   \
-        long long ctas = (long long)sms * per_sm;                                                               \
-        if (ctas * (NGG) > p.work) ctas = (p.work + (NGG) - 1) / (NGG);                                          \
-        if (int rc = launch_overlapped(attn_decode_kernel<GG, BB, NGG, KB>, dim3((unsigned)ctas), dim3(NTHR * (NGG)), smem, kvc_cu(stream), p)) return rc; \
+        long long ctas = (long long)sms * (occ < ATTN_CTAS_PER_SM ? occ : ATTN_CTAS_PER_SM);                    \
+        if (ctas > p.work) ctas = p.work;                                                                       \
+        if (int rc = launch_overlapped(attn_decode_kernel<GG, BB>, dim3((unsigned)ctas), dim3(NTHR), smem, kvc_cu(stream), p)) return rc; \
     }
-        // one query head per KV head: three groups per CTA around one copy of the tables, the K table over 14 bits,
-        // when the staging slots of three groups fit beside them (they do unless the blocks' size is unknown)
-#ifndef KVC_EXP_WBITS
-#define KVC_EXP_WBITS KVC_LUTW_BITS
-#endif
-        const size_t shared3 = sizeof(AttnBooks<KVC_EXP_WBITS>) + 3 * (sizeof(AttnSmem<1>) + attn_group_area<1>(p.slotK_bytes, p.slotV_bytes));
-        const bool wide = G == 1 && T > 0 && shared3 <= (size_t)smem_optin && !g_narrow;
-        if (bulk) { if (G == 4) KVC_AT(4, true, 1, KVC_LUT_BITS) else if (G == 2) KVC_AT(2, true, 1, KVC_LUT_BITS)
-                    else if (wide) KVC_AT(1, true, 3, KVC_EXP_WBITS) else KVC_AT(1, true, 1, KVC_LUT_BITS) }
-        else { if (G == 4) KVC_AT(4, false, 1, KVC_LUT_BITS) else if (G == 2) KVC_AT(2, false, 1, KVC_LUT_BITS)
-               else if (wide) KVC_AT(1, false, 3, KVC_EXP_WBITS) else KVC_AT(1, false, 1, KVC_LUT_BITS) }
+        if (bulk) { if (G == 4) KVC_AT(4, true) else if (G == 2) KVC_AT(2, true) else KVC_AT(1, true) }
+        else { if (G == 4) KVC_AT(4, false) else if (G == 2) KVC_AT(2, false) else KVC_AT(1, false) }
 #undef KVC_AT
         g0 += G;
     }

@@ -158,18 +158,18 @@ __device__ void build_trees(BookSmem &s) {      // s.tree was cleared to {NONE, 
     s.n_nodes = n;
 }
 
-// Decode table entry for a window w of `bits` bits (first stream bit = MSB), 32 bits:
+// Decode table entry for a KVC_LUT_BITS-bit window w (first stream bit = MSB), 32 bits:
 //   byte 0      how far the decoder state advances: (symbols << 6) | bits consumed   (0 = escape)
 //   bytes 1..3  up to three complete symbols found in the window, unused bytes 0
 // The decoder state is (position in the vector << 6) | bit offset, so one add applies an entry.
 // When no code completes inside the window (a code longer than the window, or no code at all)
 // byte 0 is 0 and the upper bytes hold the wide-tree node the window's bits lead to; the slow path
 // continues from there one bit at a time.
-__device__ uint32_t lut_entry(const uint32_t *tree, uint32_t w, int bits) {
+__device__ uint32_t lut_entry(const uint32_t *tree, uint32_t w) {
     uint32_t syms = 0, nsym = 0, used = 0;
     int idx = -1, pos = 0;
-    while (pos < bits) {
-        int bit = (w >> (bits - 1 - pos)) & 1;
+    while (pos < KVC_LUT_BITS) {
+        int bit = (w >> (KVC_LUT_BITS - 1 - pos)) & 1;
         uint32_t ch = idx == -1 ? (uint32_t)bit : ((tree[idx] >> (16 * bit)) & 0xffffu);
         pos++;
         if (ch == KVC_TREE_NONE || ch >= 512) { idx = -2; break; }     // no such code
@@ -208,13 +208,10 @@ __device__ void write_book(const BookSmem &s, uint8_t *book, int tid, int nthr) 
     uint32_t *lut = reinterpret_cast<uint32_t *>(book + KVC_BOOK_OFF_LUT);
     int no_code = 0;                                        // an entry whose window holds no complete code
     for (int w = tid; w < KVC_LUT_SIZE; w += nthr) {
-        const uint32_t e = lut_entry(s.tree, (uint32_t)w, KVC_LUT_BITS);
+        const uint32_t e = lut_entry(s.tree, (uint32_t)w);
         lut[w] = e;
         no_code |= (e & 0xffu) == 0;
     }
-    // the wide table: what the fused attention kernel reads when one copy per SM fits
-    uint32_t *lutw = reinterpret_cast<uint32_t *>(book + KVC_BOOK_OFF_LUTW);
-    for (int w = tid; w < (1 << KVC_LUTW_BITS); w += nthr) lutw[w] = lut_entry(s.tree, (uint32_t)w, KVC_LUTW_BITS);
     no_code = __syncthreads_or(no_code);
     if (tid == 0) {
         kvc_book_header *h = reinterpret_cast<kvc_book_header *>(book);

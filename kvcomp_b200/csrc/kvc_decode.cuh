@@ -125,20 +125,17 @@ __device__ __forceinline__ bool kvc_book_needs_escape(const void *book) {
 // Every round advances by at least one symbol, so the loop ends after at most 128 rounds; a corrupt
 // stream can read at most a few hundred bytes past its vector, for which the kernels keep padding
 // behind the last slot.  Returns false when the bits do not form valid codes.
-// BITS: the window of the table at lut_s (KVC_LUT_BITS, or KVC_LUTW_BITS for a book's wide table).
-template <bool ESC, int SHIFT, class Emit, bool PAIR = false, int BITS = KVC_LUT_BITS>
+template <bool ESC, int SHIFT, class Emit, bool PAIR = false>
 __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte_pos, uint32_t lut_s, uint32_t tree_s,
                                                   uint32_t base, Emit emit) {
     static_assert(SHIFT >= 0 && SHIFT <= 6, "record size");
-    static_assert(BITS >= 8 && BITS <= 16, "two windows and the bit offset must fit the 64 buffered bits");
-    constexpr uint32_t IMASK = ((1u << BITS) - 1u) << 2;   // byte offset of a table entry
     constexpr uint32_t AMASK = 0xffffffffu << SHIFT;       // drops the bit-offset bits left below the position
     const uint32_t end = (base + KVC_VEC_LEN) << 6;
     uint32_t ptr = slot_s + (byte_pos & ~3u);
     uint32_t state = (base << 6) | ((byte_pos & 3u) << 3);
     uint32_t hi = kvc_bswap(kvc_lds32(ptr)), lo = kvc_bswap(kvc_lds32(ptr + 4));
     if (PAIR && !ESC) {
-        // Two lookups per round.  The first leaves the bit offset below 32 + BITS, so the second
+        // Two lookups per round.  The first leaves the bit offset below 32 + KVC_LUT_BITS, so the second
         // one's window still lies inside (hi, lo) or (lo, next word) and needs no refill in between:
         // one refill test and one end test per pair.  The second lookup may run although the first
         // finished the vector, so up to KVC_DECODE_OVERRUN_PAIR positions past 127 are emitted.
@@ -146,12 +143,12 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
         ptr += 12;
         do {
             const uint32_t w0 = __funnelshift_l(lo, hi, state);
-            const uint32_t e0 = kvc_lds32(lut_s + ((w0 >> (32 - BITS - 2)) & IMASK));
+            const uint32_t e0 = kvc_lds32(lut_s + ((w0 >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
             emit(e0, (state >> (6 - SHIFT)) & AMASK);
             state = (uint32_t)kvc_dp4a_uu(e0, 1u, (int)state);
             const bool up = (state & 32u) != 0;
             const uint32_t w1 = __funnelshift_l(up ? nx : lo, up ? lo : hi, state);
-            const uint32_t e1 = kvc_lds32(lut_s + ((w1 >> (32 - BITS - 2)) & IMASK));
+            const uint32_t e1 = kvc_lds32(lut_s + ((w1 >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
             emit(e1, (state >> (6 - SHIFT)) & AMASK);
             state = (uint32_t)kvc_dp4a_uu(e1, 1u, (int)state);
             if (state & 32u) { hi = lo; lo = nx; nx = kvc_bswap(kvc_lds32(ptr)); ptr += 4; state -= 32u; }
@@ -165,7 +162,7 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
 #pragma unroll
       for (int rep = 0; rep < KVC_DECODE_UNROLL; rep++) {             // the end test runs once per UNROLL lookups
         const uint32_t win = __funnelshift_l(lo, hi, state);          // the shift uses the low 5 bits
-        const uint32_t e = kvc_lds32(lut_s + ((win >> (32 - BITS - 2)) & IMASK));
+        const uint32_t e = kvc_lds32(lut_s + ((win >> (32 - KVC_LUT_BITS - 2)) & ((KVC_LUT_SIZE - 1) << 2)));
         if (!ESC || (e & 0xffu) != 0) {
             emit(e, (state >> (6 - SHIFT)) & AMASK);
             state = (uint32_t)kvc_dp4a_uu(e, 1u, (int)state);         // state += byte 0 of e, off the integer ALU pipe
@@ -173,7 +170,7 @@ __device__ __forceinline__ bool kvc_decode_vector(uint32_t slot_s, uint32_t byte
             uint32_t node = e >> 8, sym = 0;
             bool found = false;
             const uint32_t a = (state >> (6 - SHIFT)) & AMASK;
-            state += BITS;
+            state += KVC_LUT_BITS;
             for (int guard = 0; guard < 40; guard++) {
                 if (state & 32u) { hi = lo; lo = kvc_bswap(nxt); nxt = kvc_lds32(ptr); ptr += 4; state -= 32u; }
                 if (node >= 512u) break;

@@ -369,11 +369,10 @@ def attn_decode(kcache, vcache, T, B, Hkv, q, scaling, ktail=None, vtail=None, o
     return out, status
 
 
-def attn_debug(wait_limit=0, starve=False, narrow=False):
-    """Diagnostics of the attention kernel (kvc_attn_debug): the bound of its staging waits, the switch that
-    lets a wait run out, and `narrow`, which keeps the kernel on per-CTA 12-bit tables even where one wide
-    table per SM would be used.  No arguments restore the defaults."""
-    _lib.load().kvc_attn_debug(int(wait_limit), int(bool(starve)) | (2 if narrow else 0))
+def attn_debug(wait_limit=0, starve=False):
+    """Diagnostics of the attention kernel's bounded staging waits (kvc_attn_debug); (0, False) restores
+    the defaults."""
+    _lib.load().kvc_attn_debug(int(wait_limit), int(bool(starve)))
 
 
 def attn_decode_static(kcache, vcache, T, B, Hkv, q, scaling, out, ktail=None, vtail=None, splits=0, status=None):

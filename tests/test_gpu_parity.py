@@ -438,31 +438,6 @@ def test_attn_decode_phi3_settings(ops, B, Hkv, Hq, T, Tr):
     assert_attn_close(out, O)
 
 
-def test_attn_decode_shared_wide_table_equals_per_cta_tables(ops):
-    """With one query head per KV head the kernel runs three groups of 256 threads per SM around one copy of
-    the tables, the K table over 14 bits; the per-CTA 12-bit form is kept for caches whose block size is not
-    known.  Both read the same codes and sum the same integers: same bits."""
-    T, B, H = 1536, 2, 6
-    k, v, q = synth(T + 50, B, H, seed=45)
-    rk, rv, kc, vc = _caches(ops, k[:T], v[:T], orc.MODE_CHANNEL, orc.MODE_TOKEN, 0.05, 0.1, 64, False)
-    scaling = 1.0 / math.sqrt(128)
-    outs = []
-    for narrow in (False, True):
-        ops.attn_debug(narrow=narrow)
-        try:
-            for splits in (0, 1, 3):
-                out, st = ops.attn_decode(kc, vc, T, B, H, dev(q), scaling, dev(k[T:]), dev(v[T:]), splits=splits)
-                assert ops.read_status(st) == 0
-                outs.append(out)
-        finally:
-            ops.attn_debug()
-    for a, b in zip(outs[:3], outs[3:]):
-        assert torch.equal(a, b)
-    O = orc.attention(*_oracle_q(rk, T, B, H, orc.MODE_CHANNEL, 64, False), *_oracle_q(rv, T, B, H, orc.MODE_TOKEN, 128, False),
-                      q, scaling, k[T:], v[T:])
-    assert_attn_close(outs[0], O)
-
-
 def test_attn_decode_llama7b_shape_small(ops):
     """The Llama-2-7B-shaped configuration with a short context: batch 8, 32 heads (MHA), K per channel
     at 0.05, V per token at 0.1, block 64."""
