@@ -554,6 +554,7 @@ struct alignas(32) AttnSmem {                     // followed in shared memory b
     uint32_t nbK[4], nbV[4];          // byte counts of the staged blocks
     int okK[4], okV[4];
     int next_j;                       // item the CTA drew for after the current one
+    int dead;                         // a staging wait ran out: the CTA takes no further item
 };
 
 struct AttnParams {
@@ -585,9 +586,13 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     uint32_t *const myrow = reinterpret_cast<uint32_t *>(slotsV + 4 * p.slotV_bytes + SLOT_PAD) + threadIdx.x * (ROW_STRIDE / 4);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = tid >> 6, v = tid & 63;
     const int grp = tid >> 7, ch = tid & 127;
-    // launched with programmatic stream serialisation: nothing in memory is touched before the kernel
-    // ahead of this one in the stream has completed
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Launched with programmatic stream serialisation.  This kernel's own set-up -- the books' tables, the first
+    // blocks, the first tile's metadata: cache data that no kernel of a decode step writes -- runs before
+    // griddepcontrol.wait, i.e. possibly while the kernel ahead of it in the stream (the merge of the layer
+    // before, which lets its dependents start early) still runs.  What that kernel or the one before it may
+    // write (the query, the scheduling counters, the workspace, the output, the status word) is touched after
+    // the wait.  (Letting this kernel's own dependents start early was measured: their waiting CTAs slow the
+    // launch by a tenth.)
     // shapes fit 32 bits (the host checks): 64-bit arithmetic only where block ids and addresses are formed
     const int T = (int)p.T, B = (int)p.B, Hkv = (int)p.Hkv, Hq = (int)p.Hq;
     const int cols = B * Hkv, Gt = Hq / Hkv;
@@ -631,7 +636,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     const bool any_tiles = have && it.t_lo < it.t_hi;      // items are empty only when the cache has no compressed part
 
     if (BULK) {
-        if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); }
+        if (tid == 0) { kvc_mbar_init(&sm.bar[0], 1); kvc_mbar_init(&sm.bar[1], 1); kvc_mbar_fence_init(); sm.dead = 0; }
         __syncthreads();
         if (warp == 0 && any_tiles) {
             stage_bulk(p.k, validK(true, it.t_lo, lane & 3), blkK_of(it.col, it.t_lo, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, sm.nbK, &sm.bar[0], lane, p.starve != 0);
@@ -687,6 +692,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             if (idx < G * 128) sm.qf[idx] = kvc_scale_value(qn[i]) * p.scaling;
         }
     };
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (have) q_fetch(it.col);
 
     uint32_t par = 0;                                      // bit 0 / bit 1: parity of the staging phase the K / V barrier is waited for next
@@ -702,8 +708,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
 #pragma unroll
     for (int g = 0; g < G; g++) { m_run[g] = -CUDART_INF_F; l_run[g] = 0.f; acc[g] = 0.f; }
 
-    int tile = it.t_lo;
-    for (; tile < it.t_hi; tile++) {
+    for (int tile = it.t_lo; tile < it.t_hi; tile++) {
         const long long tok0 = (long long)tile * 256, t = tok0 + tid;
         const long long blkK = (tok0 / 64 + sub) * cols + col;
         const long long gI = tok0 / 128 + grp;
@@ -720,10 +725,10 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
             if (actV) { uint32_t ld, nb; bool ok = stage(p.v, blkV, slotsV + sub * p.slotV_bytes, &ld, &nb, v); if (v == 0) { sm.leadV[sub] = ld; sm.nbV[sub] = nb; sm.okV[sub] = ok; } }
         }
         k_weights_build<G, ROWS>(sm.w, sm.kstep, sm.zp, sm.qf, cur.ku, km.sc != 0, km.min_bytes, tok0, T, tid);
-        // A wait that runs out: the thread does not decode, and at the phase's closing barrier (which also joins
-        // the threads' verdicts) the CTA stops before it arms the barrier that never completed again: it issues
-        // no further copies and takes no further tiles; what it had in flight is waited for once more,
-        // bounded, before it returns.
+        // A wait that runs out: the thread does not decode.  The warp that issues the copies looks at its own
+        // verdict: a barrier whose phase it did not see complete is never armed again (a second arrival on an
+        // open phase is an error), and the CTA is marked; it takes no further item, and what it had in flight
+        // is waited for once more, bounded, before it returns.
         bool k_landed = true;
         if (BULK) {
             k_landed = kvc_mbar_wait(&sm.bar[0], par & 1u, p.wait_limit);
@@ -750,14 +755,15 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         // ---- online softmax over the tile
 #pragma unroll
         for (int g = 0; g < G; g++) { float mx = kvc_warp_max(s[g]); if (lane == 0) sm.red[0][warp * G + g] = mx; }
-        // every thread is done with the K slots (and: did any thread's K wait run out?)
-        if (BULK) { if (__syncthreads_or(flags & KVC_FLAG_WAIT_TIMEOUT)) break; }
-        else __syncthreads();
+        __syncthreads();                                   // also: every thread is done with the K slots
         // the next tile's per-thread metadata is asked for now and first touched when that tile begins: it is in
         // flight during the V phase only, and the K decode above ran without its registers
         load_meta(n_on, n_col, n_tile, nxt);
-        if (BULK && warp == 0)                             // next tile's K blocks land during the V phase
-            stage_bulk(p.k, validK(n_on, n_tile, lane & 3), blkK_of(n_col, n_tile, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, sm.nbK, &sm.bar[0], lane, p.starve != 0);
+        if (BULK && warp == 0) {                           // next tile's K blocks land during the V phase
+            if (__all_sync(0xffffffffu, k_landed))
+                stage_bulk(p.k, validK(n_on, n_tile, lane & 3), blkK_of(n_col, n_tile, lane & 3), slotsK + (lane & 3) * p.slotK_bytes, sm.leadK, sm.okK, sm.nbK, &sm.bar[0], lane, p.starve != 0);
+            else if (lane == 0) sm.dead = 1;
+        }
         float alpha[G], wv[G];
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -806,14 +812,14 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         }
 #pragma unroll
         for (int g = 0; g < G; g++) acc[g] = fmaf(acc[g], alpha[g], dv[g]);
-        // every thread is done with the V slots, weights and sums; did any thread's wait run out?
-        if (BULK) { if (__syncthreads_or(flags & KVC_FLAG_WAIT_TIMEOUT)) break; }   // (the K copy issued above is waited for at the end)
-        else __syncthreads();
-        if (BULK && warp == 0)                             // next tile's V blocks land during its K phase
-            stage_bulk(p.v, validV(n_on, n_tile, lane & 3), blkV_of(n_col, n_tile, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, sm.nbV, &sm.bar[1], lane, p.starve != 0);
+        __syncthreads();                                   // every thread is done with the V slots, weights and sums
+        if (BULK && warp == 0) {                           // next tile's V blocks land during its K phase
+            if (__all_sync(0xffffffffu, v_landed))
+                stage_bulk(p.v, validV(n_on, n_tile, lane & 3), blkV_of(n_col, n_tile, lane & 3), slotsV + (lane & 3) * p.slotV_bytes, sm.leadV, sm.okV, sm.nbV, &sm.bar[1], lane, p.starve != 0);
+            else if (lane == 0) sm.dead = 1;
+        }
         cur = nxt;
     }
-    if (BULK && tile < it.t_hi) break;                     // a wait ran out: no partial result is written, the status word says why
 
     // ---- uncompressed tail (the recent window), handled with the column's last tiles: dense fp16 rows
     if (p.Tr > 0 && it.t_hi == n_tiles) {
@@ -902,6 +908,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     }
     if (draw && tid == 0) sm.next_j = drawn;
     __syncthreads();                                       // the sums are read before the next column's weights overwrite them
+    if (BULK && sm.dead != 0) break;                       // a staging wait ran out: the status word says so, the item's result is void
     const int j_n2 = draw ? 2 * P + sm.next_j : j_n1 + 1;
     it = nit; have = have_next; j_it = j_n1; j_n1 = j_n2;
     have_next = have && item_of(j_n1, nit);
@@ -918,23 +925,53 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     }
 }
 
-// Merges the `splits` partial results of every head: grid = heads, 128 threads = channels.
+// Merges the `splits` partial results of every head: grid = heads, 128 threads = channels.  The loads of the
+// partial results are issued in batches before any is used (a loop whose every load waits for the one
+// before costs a memory latency per split).
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits) {
+    __shared__ float sm_red[4], sm_e[128];
     const float *src = ws_part + (size_t)blockIdx.x * splits * ATTN_PART_FLOATS;
-    const int tid = threadIdx.x;
-    // launched with programmatic stream serialisation: the CTAs may be resident before the attention
-    // kernel has finished; its partial results are complete and visible after this wait
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // launched with programmatic stream serialisation: the kernel behind this one in the stream may set up
+    // while this one runs (it touches nothing this one writes before its own wait), and this one's CTAs may be
+    // resident before the attention kernel has finished; its partial results are complete and visible after the wait
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    float M = -CUDART_INF_F;
-    for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, src[s2 * ATTN_PART_FLOATS]);
-    float L = 0.f, O = 0.f;
-    for (int s2 = 0; s2 < splits; s2++) {
-        const float *pp = src + s2 * ATTN_PART_FLOATS;
-        const float m2 = pp[0];
-        const float e = m2 == -CUDART_INF_F ? 0.f : __expf(m2 - M);
-        L = fmaf(pp[1], e, L);
-        O = fmaf(pp[4 + tid] + pp[4 + 128 + tid], e, O);
+    float M = -CUDART_INF_F;                              // the maximum over all partial results
+    for (int s2 = tid; s2 < splits; s2 += 128) M = fmaxf(M, src[(size_t)s2 * ATTN_PART_FLOATS]);
+    M = kvc_warp_max(M);
+    if (lane == 0) sm_red[warp] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3]));
+    float O = 0.f, L = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 128) {
+        const int ns = min(128, splits - s0);
+        __syncthreads();                                  // the weights of the batch before are spent
+        float e = 0.f;
+        if (tid < ns) {
+            const float *pp = src + (size_t)(s0 + tid) * ATTN_PART_FLOATS;
+            const float m2 = pp[0];
+            e = m2 == -CUDART_INF_F ? 0.f : __expf(m2 - M);
+            L = fmaf(pp[1], e, L);
+        }
+        sm_e[tid] = e;
+        __syncthreads();
+        for (int i0 = 0; i0 < ns; i0 += 8) {              // channel tid of 8 partial results, all loads in flight together
+            float a[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const float *pp = src + (size_t)(s0 + min(i0 + k, ns - 1)) * ATTN_PART_FLOATS;
+                a[k] = pp[4 + tid] + pp[4 + 128 + tid];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) if (i0 + k < ns) O = fmaf(a[k], sm_e[i0 + k], O);
+        }
     }
+    L = kvc_warp_sum(L);
+    __syncthreads();
+    if (lane == 0) sm_red[warp] = L;
+    __syncthreads();
+    L = (sm_red[0] + sm_red[1]) + (sm_red[2] + sm_red[3]);
     out[(size_t)blockIdx.x * 128 + tid] = __float2half_rn(O / L);
 }
 
@@ -1052,6 +1089,9 @@ constexpr int ATTN_ITEMS_PER_CTA = 4;
 // end of every column short runs of half that, enough of them that each resident CTA finds about two
 // short items to finish with.  The short items are handed out last (the item order puts them behind
 // all long ones), so the CTAs of a launch end within one short item of each other.
+#ifndef KVC_EXP_SHORT
+#define KVC_EXP_SHORT 4
+#endif
 struct RunPlan { int tps, long_runs, short_tiles, splits; };
 static RunPlan plan_runs(long long n_tiles, long long cols, int sm_count) {
     RunPlan r = {1, 1, 1, 1};
@@ -1061,7 +1101,7 @@ static RunPlan plan_runs(long long n_tiles, long long cols, int sm_count) {
     if (tps < 1) tps = 1;
     if (tps > n_tiles) tps = n_tiles;
     // (items of a single tile pay the per-item work too often: measured slower than no short runs at all)
-    long long short_tiles = tps >= 4 ? tps / 2 : tps;
+    long long short_tiles = tps >= KVC_EXP_SHORT ? tps / 2 : tps;
     long long short_region = 0;                                      // tiles of a column cut into short runs
     if (short_tiles < tps) {
         short_region = (2 * P * short_tiles + cols - 1) / cols;       // about two short items per CTA over all columns
