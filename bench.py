@@ -19,6 +19,7 @@ Prints ONE JSON line (rank 0).  Besides the headline it carries
                  tensor at five error bounds: encode / decode GB/s, compression ratio, bits per symbol
   gpu_reference  (N = 1, when baseline/_ref/kvcomp_cuda.so is present) the reference's own fused K and
                  V kernels timed beside this library's on the reference's own shapes
+  other_workloads (N = 1) the two grouped-query configurations, a few layers each: per-layer time and roofline fraction
   strong         (N > 1) the Mistral-shaped GQA cache with its KV heads split over the ranks and one NCCL
                  all-gather of the outputs per step, against the same layers on one GPU
   cpu_baseline   (N = 1) the CPU restatement of the reference's path on a bounded sample
@@ -391,6 +392,41 @@ def gpu_reference(ops, torch, device, seed, ctxs=(2048, 4096, 8192, 16384), H=32
             "rows": rows}
 
 
+def side_workloads(ops, torch, device, seed, names=("c2", "c3"), layers=2):
+    """The grouped-query configurations on one GPU, a few layers each (their full caches are for several GPUs):
+    per-layer time of the fused kernel, its fraction of the HBM roofline on compressed bytes, fp16-equivalent
+    bytes served."""
+    out = {}
+    peak, _ = peaks()
+    for name in names:
+        cfg = dict(WORKLOADS[name]); cfg["layers"] = layers
+        T, B, Hkv, Hq = cfg["T"], cfg["B"], cfg["Hkv"], cfg["Hq"]
+        built = [build_layer(ops, torch, cfg, l, seed, device) for l in range(layers)]
+        ws = ops.attn_workspace(B, Hq, ops.attn_splits(T, B, Hkv), device)
+        status = ops.new_status(device)
+        outs = torch.empty((layers, B, Hq, 128), dtype=torch.float16, device=device)
+        scaling = 1.0 / math.sqrt(128)
+
+        def step():
+            for i, (caches, _, q, _) in enumerate(built):
+                ops.attn_decode(caches[0], caches[1], T, B, Hkv, q, scaling, out=outs[i], workspace=ws, status=status)
+        for _ in range(3):
+            step()
+        blocks = timed_blocks(torch, step, 5, torch.cuda.synchronize, min_seconds=0.2)
+        ops.read_status(status, what="attn_decode")
+        ms_layer = float(np.median(blocks)) / 5 / layers
+        alg = float(np.mean([algorithmic_bytes(b[3], cfg) for b in built]))
+        out[name] = {"workload": name + ": " + cfg["desc"], "layers_timed": layers, "ms_per_layer": ms_layer,
+                     "tokens_per_s_full_model": B / (ms_layer * WORKLOADS[name]["layers"] / 1e3),
+                     "algorithmic_bytes_per_layer": alg, "achieved_GBps": alg / ms_layer / 1e6, "frac_of_hbm_peak": alg / ms_layer / 1e6 / peak,
+                     "effective_fp16_GBps": 2 * 2 * T * B * Hkv * 128 / ms_layer / 1e6,
+                     "launches_per_layer": sum(1 for _ in _chunks(Hq // Hkv)) + 1,
+                     "bits_per_symbol": {k: float(np.mean([8.0 * b[3][k]["encoded"] / b[3][k]["symbols"] for b in built])) for k in ("k", "v")}}
+        del built, ws, outs
+        torch.cuda.empty_cache()
+    return out
+
+
 def timed_blocks(torch, step, steps, barrier, min_seconds=MIN_TIMED_SECONDS, max_blocks=MAX_BLOCKS, world_reduce=None):
     """Blocks of exactly `steps` steps, each bracketed by barrier + synchronize on both sides and timed with
     CUDA events on the launching stream; repeated until `min_seconds` of device time are covered.  Every
@@ -690,6 +726,8 @@ def main():
                            "by_error_bound": agg, "gpu_launches": codec_launches}
         if world == 1:
             extras["gpu_reference"] = gpu_reference(ops, torch, device, args.seed)
+            if args.workload == "c1":
+                extras["other_workloads"] = side_workloads(ops, torch, device, args.seed)
         elif not heads_mode:
             extras["strong"] = strong_record(args, ops, torch, dist, device, rank, world, barrier, reduce_max)
 
