@@ -219,12 +219,22 @@ class KVCompCtx:
         bsz, tsz, _, cap = ops.buffer_sizes(T, cols * self.head_dim, self.is_k)
         bi = self._bi.reserve(bsz, self.device)
         ti = self._ti.reserve(tsz // 2, self.device)
-        enc = self._enc.reserve(cap, self.device)                  # the reference reserves numel bytes too
-        total = torch.tensor([0, self.max_block_bytes], dtype=torch.int64, device=self.device)
-        total, st_e = ops.encode(codes, self.is_k, self.book.encode_table(), bi, ti, enc,
-                                 base_offset=self._enc.n, total=total)
-        n_bytes, max_block = (int(v) for v in total.tolist())      # synchronises, as the reference does
-        flags = ops.read_status(st_e, raise_on_fatal=False)
+        # The reference reserves one byte per symbol (numel) for every store (kernels.cu:903); the stream
+        # needs a fraction of that, so room is reserved from the density seen so far (8 bits per symbol at
+        # first) with a quarter on top, and the store is repeated with the full reserve in the rare case
+        # that the encoder reports the room as exceeded.
+        seen = self.encoded_ctx_len * cols * self.head_dim
+        est = cap if seen == 0 else min(cap, int(1.25 * self._enc.n / seen * codes.numel()) + 4096)
+        for room in (est, cap):
+            enc = self._enc.reserve(room, self.device)
+            total = torch.tensor([0, self.max_block_bytes], dtype=torch.int64, device=self.device)
+            total, st_e = ops.encode(codes, self.is_k, self.book.encode_table(), bi, ti, enc,
+                                     base_offset=self._enc.n, total=total)
+            n_bytes, max_block = (int(v) for v in total.tolist())      # synchronises, as the reference does
+            flags = ops.read_status(st_e, raise_on_fatal=False)
+            if not (flags & ops._lib.FLAG_STREAM_FULL) or room == cap:
+                break
+            self.stream_retries = getattr(self, "stream_retries", 0) + 1
         if flags & ops._lib.FLAG_SYMBOL_MISSING:
             return False
         ops.read_status(st_e, what="entropy_encode")

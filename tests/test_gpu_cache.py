@@ -486,3 +486,35 @@ def test_rope_store_equals_torch_ops():
         want = apply_rotary_pos_emb_single(x, cos, sin).permute(2, 0, 1, 3).contiguous()
         assert torch.equal(ops.rope_store(x, cos, sin), want)
         assert torch.equal(ops.rope_store(x, cos.expand(B, -1, -1).contiguous(), sin.expand(B, -1, -1).contiguous()), want)
+
+
+def test_ctx_stream_room_follows_the_density_seen(cfg):
+    """The stream's arena grows by what the data needs (estimated from the density so far), not by one byte
+    per symbol as the reference reserves; when a store is denser than the estimate allows, the encoder
+    reports the room as exceeded and the store is repeated with the full reserve.  Same codes either way."""
+    from kvcomp_b200.cache import KVCompCtx
+    cfg(kmode="ChannelQuant", krec=0, vrec=0, quant_per_sequence=True, wide_min_ints=True)
+    T, B, H = 512, 1, 4
+    k, _, _ = synth(T, B, H, seed=16)
+    wide = k.cuda()
+    narrow = wide.clone()
+    # every channel at its centre, two tokens per block keep the channel's range: nearly all codes are the
+    # book's shortest (3 bits against 4.2 on average)
+    narrow[:256] = ((wide.amin(dim=0, keepdim=True).float() + wide.amax(dim=0, keepdim=True).float()) / 2).half()
+    narrow[0:256:64] = wide.amin(dim=0, keepdim=True)
+    narrow[1:256:64] = wide.amax(dim=0, keepdim=True)
+    ctx = KVCompCtx(True, B, H, 128, 0.05)
+    ctx.build_codebook([wide])
+    ctx.store(narrow[:256])
+    low = ctx.encoded_data.numel()
+    assert ctx._enc.buf.numel() == 256 * B * H * 128             # the first store cannot know better
+    ctx.store(wide[256:])                                          # denser than the estimate allows: stored on the second try
+    assert ctx.encoded_data.numel() > 2.3 * low and getattr(ctx, "rebooks", 0) == 0 and ctx.stream_retries == 1
+    decoded, _ = ctx.get_decode_quant_ints()
+    want = np.concatenate([orc.quant(x.cpu().numpy(), orc.MODE_CHANNEL, 64, 0.05, False)[0] for x in (narrow[:256], wide[256:])])
+    assert np.array_equal(decoded.reshape(T, B, H, 128).cpu().numpy(), want)
+    # a third store of the usual density fits the estimate: the arena grows by far less than a byte per symbol
+    before = ctx._enc.buf.numel()
+    ctx.store(wide[:256])
+    assert ctx._enc.buf.numel() - before < 256 * B * H * 128
+    assert ctx.compressed_ctx_len == 768
