@@ -97,3 +97,23 @@ def test_no_cpu_path():
         ops.quantize(torch.zeros(64, 1, 1, 128, dtype=torch.float16), 0, 64, 0.05)
     with pytest.raises(_lib.KvcError):
         ops.histogram(torch.zeros(64, dtype=torch.uint8))
+
+
+def test_header_is_valid_c_and_links_from_c(lib, tmp_path):
+    """include/kvcomp_b200.h compiled as C by gcc and linked against the library: the boundary a cgo, JNI or
+    FFI binding would use.  Host-only entry points are called; no kernel is launched."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if not gcc:
+        pytest.skip("no C compiler")
+    exe = str(tmp_path / "cabi_check")
+    libdir = os.path.dirname(_lib.lib_path())
+    r = subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-I", os.path.join(REPO, "include"),
+                        os.path.join(REPO, "tests", "cabi_check.c"), "-L", libdir, "-lkvcomp_b200",
+                        "-Wl,-rpath," + libdir, "-o", exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([exe], capture_output=True, text=True)
+    import ctypes
+    want = "ok %d %d %d" % (_lib.BOOK_BYTES, ctypes.sizeof(_lib.Cache), ctypes.sizeof(_lib.QMeta))
+    assert r.returncode == 0 and r.stdout.strip() == want, (r.returncode, r.stdout, r.stderr, want)
