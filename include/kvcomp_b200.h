@@ -192,6 +192,13 @@ int kvc_encode(const uint8_t *codes, int64_t T, int64_t cols, int is_k,
                unsigned long long *total_bytes, void *workspace, int64_t workspace_bytes,
                int32_t *status, kvc_stream_t stream);
 
+/* Diagnostics, no counterpart in the reference.  The encoder's CTAs learn their block's byte offset from
+ * the blocks before them and wait for each at most `wait_limit` polls (0 = the default of 2^21); a wait
+ * that runs out raises KVC_FLAG_WAIT_TIMEOUT, the block and every later one write nothing, and the call
+ * returns.  starve != 0 makes the first block keep its byte count to itself, so that a test can see the
+ * waits run out; the stream of such a call is undefined.  Process-wide, read at every launch. */
+void kvc_encode_debug(int wait_limit, int starve);
+
 /* k_/v_entropy_decode_cuda_export (kernels.cu:1013-1087): stream -> u8 codes [T, cols, 128].
  * block_info offsets are relative to `encoded`. */
 int kvc_decode(const uint8_t *encoded, int64_t encoded_bytes, const void *block_info,

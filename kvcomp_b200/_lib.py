@@ -67,6 +67,7 @@ _SIGNATURES = {
     "kvc_build_codebook": (_i32, [_vp, _vp, _vp]),
     "kvc_book_from_tree": (_i32, [_vp, _i64, _vp, _vp]),
     "kvc_encode_workspace": (_i64, [_i64, _i64, _i32]),
+    "kvc_encode_debug": (None, [_i32, _i32]),
     "kvc_encode": (_i32, [_vp, _i64, _i64, _i32, _vp, _i32, _u32, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp]),
     "kvc_decode": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp]),
     "kvc_decode_bounded": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _u32, _vp, _vp, _vp]),

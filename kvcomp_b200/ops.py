@@ -369,6 +369,12 @@ def attn_decode(kcache, vcache, T, B, Hkv, q, scaling, ktail=None, vtail=None, o
     return out, status
 
 
+def encode_debug(wait_limit=0, starve=False):
+    """Diagnostics of the encoder's bounded waits between blocks (kvc_encode_debug); (0, False) restores the
+    defaults."""
+    _lib.load().kvc_encode_debug(int(wait_limit), int(bool(starve)))
+
+
 def attn_debug(wait_limit=0, starve=False):
     """Diagnostics of the attention kernel's bounded staging waits (kvc_attn_debug); (0, False) restores
     the defaults."""

@@ -264,6 +264,27 @@ def test_encode_base_offset_and_append(ops):
     assert off[nb] == n1
 
 
+def test_encode_wait_between_blocks_runs_out_and_returns(ops):
+    """A block's CTA learns its byte offset from the blocks before it, with bounded waits.  With the
+    diagnostic that makes the first block keep its count to itself the waits run out after a few polls:
+    the call returns, the status word carries KVC_FLAG_WAIT_TIMEOUT, and the next ordinary call writes
+    the same stream as before."""
+    T, B, H = 256, 2, 3
+    k, _, _ = synth(T, B, H, seed=23)
+    r = _pipeline(ops, k, True, orc.MODE_CHANNEL, 64, 0.05, False)
+    bi, ti, enc = torch.zeros_like(r["bi"]), torch.zeros_like(r["ti"]), torch.zeros_like(r["enc"])
+    try:
+        ops.encode_debug(wait_limit=8, starve=True)
+        total, st = ops.encode(r["codes"], True, r["book"].encode_table(), bi, ti, enc)
+        torch.cuda.synchronize()
+        assert ops.read_status(st, raise_on_fatal=False) & 0x400
+    finally:
+        ops.encode_debug()
+    total, st = ops.encode(r["codes"], True, r["book"].encode_table(), bi, ti, enc)
+    assert ops.read_status(st) & ~0x10 == 0 and int(total[0]) == r["n"]
+    assert torch.equal(enc[:r["n"]], r["enc"][:r["n"]]) and torch.equal(bi, r["bi"]) and torch.equal(ti, r["ti"])
+
+
 def test_book_from_reference_decode_tensor(ops):
     k, _, _ = synth(128, 1, 2, seed=4)
     r = _pipeline(ops, k, True, 0, 64, 0.05, True)
