@@ -604,6 +604,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling small cases)")
+    ap.add_argument("--codec-rels", default="", help="c4: comma-separated error bounds instead of the full sweep (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="leave out the codec, gpu_reference and strong sub-records")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS, help="device time the repeated timed block has to cover")
@@ -653,7 +654,8 @@ def main():
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        sweep, launches, raw = codec_sweep(ops, torch, device, args.seed + 7919 * rank, reps=max(2, args.steps // 5))
+        rels = tuple(float(r) for r in args.codec_rels.split(",")) if args.codec_rels else (0.01, 0.02, 0.05, 0.1, 0.2)
+        sweep, launches, raw = codec_sweep(ops, torch, device, args.seed + 7919 * rank, rels=rels, reps=max(2, args.steps // 5))
         clocks = sampler.stop() if rank == 0 else None
         agg = {}
         for rel, r in sweep.items():
@@ -666,7 +668,7 @@ def main():
                             encode_next_GBps=world * r["encode_next_GBps"] * r["encode_next_ms"] / e2,
                             decode_2s_GBps=world * r["decode_2s_GBps"] * r["decode_2s_ms"] / d2)
         if rank == 0:
-            head = agg.get("0.05", {})
+            head = agg.get("0.05", next(iter(agg.values())))
             peak, kind = peaks()
             per = head.get("encode_GBps", 0) / world
             print(json.dumps({

@@ -60,17 +60,52 @@ __device__ __forceinline__ uint32_t quant_one(__half x, const UnitParam &p, int 
 }
 
 // quantise 8 halves held in a uint4 -> 8 code bytes in a uint2; optional smem histogram.
-// All eight go down the common path without a test in between (a unit with scale 0 has rcp = 0 and
-// min_int = 0 there, which yields code 0 by the same arithmetic); one test at the end sends the whole
-// chunk through quant_one again if any value fell outside 0..255 or was not finite.
-__device__ __forceinline__ uint2 quant_eight(const uint4 &v, const UnitParam *p, int pstride, int *flags,
-                                             unsigned int *hist) {
+// PS: 0 = the eight values share one unit (p[0]), 1 = value i belongs to unit p[i].
+//
+// Packed path, for units whose min_int lies in -255..255 (`small_min`; mi2 holds the min_ints as fp16 pairs):
+// after the fp32 product q0 = x * (1 / scale) everything is done on two values per instruction in fp16, which
+// is what the reference's tensors hold anyway.
+//  * fp16(q0) equals the reference's fp16(x / scale) except on exact ties between two fp16 subnormals, where
+//    both round to the integer 0 (checked over every pair of fp16 values).
+//  * (qh + 1536) - 1536 in fp16 is rint(qh) for |qh| <= 512; beyond that the result stays beyond 511 in
+//    magnitude or is no integer, and with |min_int| <= 255 such a value fails the range test below.
+//  * d = r - min_int, then d + 1024 has the bit pattern 0x6400 + d for the integers 0 <= d < 1024: the code is
+//    read from the mantissa, and one mask over all eight tells whether every code is in 0..255.
+// Anything else (a value out of range, not finite, a unit with a large min_int) takes the fp32 path below it,
+// which follows the reference's arithmetic to the end.
+template <int PS>
+__device__ __forceinline__ uint2 quant_eight(const uint4 &v, const UnitParam *p, bool small_min, const __half2 *mi2,
+                                             int *flags, unsigned int *hist) {
     const __half *h = reinterpret_cast<const __half *>(&v);
+    uint2 o;
+    if (small_min) {
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&v);
+        const __half2 big = __float2half2_rn(1536.0f), nbig = __float2half2_rn(-1536.0f), k1024 = __float2half2_rn(1024.0f);
+        uint32_t u[4], odd = 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 xf = __half22float2(h2[k]);
+            const __half2 qh = __floats2half2_rn(__fmul_rn(xf.x, p[2 * k * PS].rcp), __fmul_rn(xf.y, p[(2 * k + 1) * PS].rcp));
+            const __half2 r = __hadd2(__hadd2(qh, big), nbig);
+            const __half2 t = __hadd2(__hsub2(r, mi2[k * PS]), k1024);
+            u[k] = *reinterpret_cast<const uint32_t *>(&t) - 0x64006400u;
+            odd |= u[k];
+        }
+        if ((odd & 0xff00ff00u) == 0) {
+            if (hist) {
+#pragma unroll
+                for (int k = 0; k < 4; k++) { atomicAdd(&hist[u[k] & 0xffu], 1u); atomicAdd(&hist[u[k] >> 16], 1u); }
+            }
+            o.x = __byte_perm(u[0], u[1], 0x6420);
+            o.y = __byte_perm(u[2], u[3], 0x6420);
+            return o;
+        }
+    }
     uint32_t c[8];
     uint32_t odd = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const UnitParam &u = p[i * pstride];
+        const UnitParam &u = p[i * PS];
         const float xf = __half2float(h[i]);
         const float q0 = __fmul_rn(xf, u.rcp);
         const float q1 = __fmaf_rn(__fmaf_rn(-q0, u.sf, xf), u.rcp, q0);
@@ -84,17 +119,17 @@ __device__ __forceinline__ uint2 quant_eight(const uint4 &v, const UnitParam *p,
     }
     if (odd > 255u) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) c[i] = quant_one(h[i], p[i * pstride], flags);
+        for (int i = 0; i < 8; i++) c[i] = quant_one(h[i], p[i * PS], flags);
     }
     if (hist) {
 #pragma unroll
         for (int i = 0; i < 8; i++) atomicAdd(&hist[c[i]], 1u);
     }
-    uint2 o;
     o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
     o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
     return o;
 }
+__device__ __forceinline__ bool small_min_int(float mi) { return mi >= -255.0f && mi <= 255.0f; }
 
 // The CTA's bins are private to each warp (sh[warp][256]): fewer lanes meet on a counter.
 __device__ __forceinline__ void hist_clear(unsigned int *sh, int tid, int nthr) {
@@ -122,7 +157,8 @@ __device__ __forceinline__ void minmax8(const uint4 &v, float &mn, float &mx) {
 
 // ---- ChannelQuant (utils/compute.py:140): one unit per (token block, b, h, channel) -------------
 // CTA = one (j, b, h) tile of blk tokens x 128 channels; thread = 8 channels x every 8th token.
-// (Walking several tiles per CTA to clear and flush the histogram bins less often measured slower.)
+// (Measured slower: several tiles per CTA with one flush of the bins; tiles of two or four heads; the tile's
+// rows held in registers between the two passes; four rows in flight per thread in either pass.)
 __global__ void __launch_bounds__(128) quant_channel_kernel(
     const __half *__restrict__ x, long long B, long long H, int blk, float rel,
     uint8_t *__restrict__ codes, void *__restrict__ min_int, int min_bytes, __half *__restrict__ scale,
@@ -167,9 +203,16 @@ __global__ void __launch_bounds__(128) quant_channel_kernel(
     UnitParam p[8];
 #pragma unroll
     for (int k = 0; k < 8; k++) { p[k].sf = smn[0][cg * 8 + k]; p[k].mi = smn[1][cg * 8 + k]; p[k].rcp = smn[2][cg * 8 + k]; }
+    bool small = true;
+    __half2 mi2[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        small = small && small_min_int(p[2 * k].mi) && small_min_int(p[2 * k + 1].mi);
+        mi2[k] = __floats2half2_rn(p[2 * k].mi, p[2 * k + 1].mi);
+    }
     for (int i = r; i < blk; i += 8) {
         uint4 v = *reinterpret_cast<const uint4 *>(x + base + i * row_stride);
-        uint2 o = quant_eight(v, p, 1, &flags, ghist ? shist : nullptr);
+        uint2 o = quant_eight<1>(v, p, small, mi2, &flags, ghist ? shist : nullptr);
         *reinterpret_cast<uint2 *>(codes + base + i * row_stride) = o;
     }
     if (flags) atomicOr(status, flags);
@@ -217,9 +260,11 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(
         __half sc;
         UnitParam p = unit_param(mn, mx, rel, &sc, &flags);
         if (gl == 0) { scale[u] = sc; store_min(min_int, min_bytes, u, p.mi, &flags); }
+        const bool small = small_min_int(p.mi);
+        const __half2 mi2 = __float2half2_rn(p.mi);
         for (long long k = gl; k < chunks; k += GROUP) {
             uint4 v = *reinterpret_cast<const uint4 *>(xu + k * 8);
-            uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist + warp * 256 : nullptr);
+            uint2 o = quant_eight<0>(v, &p, small, &mi2, &flags, ghist ? shist + warp * 256 : nullptr);
             *reinterpret_cast<uint2 *>(codes + u * ulen + k * 8) = o;
         }
     }
@@ -270,9 +315,11 @@ __global__ void __launch_bounds__(WARPS == 1 ? 256 : WARPS * 32) quant_contig_re
         __half sc;
         const UnitParam p = unit_param(mn, mx, rel, &sc, &flags);
         if (gt == 0) { scale[u] = sc; store_min(min_int, min_bytes, u, p.mi, &flags); }
+        const bool small = small_min_int(p.mi);
+        const __half2 mi2 = __float2half2_rn(p.mi);
 #pragma unroll
         for (int i = 0; i < CH; i++) {
-            const uint2 o = quant_eight(v[i], &p, 0, &flags, ghist ? shist + warp * 256 : nullptr);
+            const uint2 o = quant_eight<0>(v[i], &p, small, &mi2, &flags, ghist ? shist + warp * 256 : nullptr);
             *reinterpret_cast<uint2 *>(codes + u * ULEN + (long long)(i * GT + gt) * 8) = o;
         }
     }
@@ -363,9 +410,11 @@ __global__ void __launch_bounds__(256) quant_block_apply_kernel(
     p.sf = __uint_as_float(ws[2 * u]); p.mi = __uint_as_float(ws[2 * u + 1]);
     p.rcp = (p.sf == 0.0f || p.sf != p.sf) ? 0.0f : __frcp_rn(p.sf);
     int flags = 0;
+    const bool small = small_min_int(p.mi);
+    const __half2 mi2 = __float2half2_rn(p.mi);
     for (long long k = tid; k < row_len / 8; k += 256) {
         uint4 v = *reinterpret_cast<const uint4 *>(x + row * row_len + k * 8);
-        uint2 o = quant_eight(v, &p, 0, &flags, ghist ? shist + (tid >> 5) * 256 : nullptr);
+        uint2 o = quant_eight<0>(v, &p, small, &mi2, &flags, ghist ? shist + (tid >> 5) * 256 : nullptr);
         *reinterpret_cast<uint2 *>(codes + row * row_len + k * 8) = o;
     }
     if (flags) atomicOr(status, flags);

@@ -127,6 +127,41 @@ def test_quantize_matches_torch_ops_on_gpu(ops):
         assert torch.equal(mi2.view(-1).float(), mi.reshape(-1).float())
 
 
+@pytest.mark.parametrize("mode,block,shared", [(orc.MODE_CHANNEL, 64, False), (orc.MODE_TOKEN, 128, False),
+                                               (orc.MODE_VECTOR, 64, False), (orc.MODE_BLOCK, 64, True)])
+def test_quantize_every_arithmetic_path(ops, mode, block, shared):
+    """Units whose min_int is small take the packed fp16 path, units far from zero (min_int beyond +-255) the
+    fp32 one, and single values that leave 0..255 are redone one by one: data that mixes all of them, fp16
+    subnormals, magnitudes near the top of fp16 and constant units, against the checker."""
+    rng = np.random.default_rng(77)
+    T, B, H = 128, 2, 4
+    # spread and centre are constant over a unit of the mode under test
+    shape = {orc.MODE_CHANNEL: (1, B, H, 128), orc.MODE_TOKEN: (T, B, 1, 1), orc.MODE_VECTOR: (T, B, H, 1),
+             orc.MODE_BLOCK: (T // block, 1, 1, 1)}[mode]
+    lo = 1e-6 if mode == orc.MODE_CHANNEL else 1e-3
+    spread = np.exp(rng.uniform(np.log(lo), np.log(50.0), shape)).astype(np.float32)
+    centre = spread * rng.choice([0.0, 0.0, 3.0, -8.0, 40.0, -300.0], shape).astype(np.float32)
+    if mode == orc.MODE_BLOCK:
+        spread, centre = np.repeat(spread, block, axis=0), np.repeat(centre, block, axis=0)
+    x = np.clip(rng.standard_normal((T, B, H, 128)).astype(np.float32) * spread + centre, -60000, 60000)
+    x[:, 0, 1, 5] = x[0, 0, 1, 5] if mode == orc.MODE_CHANNEL else x[:, 0, 1, 5]      # a constant channel
+    if mode in (orc.MODE_TOKEN, orc.MODE_VECTOR):
+        x[5, 1] = 0.0                                        # constant units
+    x = x.astype(np.float16)
+    seen = set()
+    for rel in (0.05, 0.011):
+        codes, mi, sc, m, deg = orc.quant(x, mode, block, rel, shared)
+        hist = torch.zeros(256, dtype=torch.int64, device="cuda")
+        c2, mi2, sc2, spec, st = ops.quantize(dev(x), mode, block, rel, shared, min_dtype=torch.int16, hist=hist)
+        ops.read_status(st, raise_on_fatal=False)
+        assert np.array_equal(sc2.cpu().numpy().view(np.uint16), sc.view(np.uint16))
+        assert np.array_equal(mi2.cpu().numpy(), mi)
+        assert np.array_equal(c2.cpu().numpy(), codes)
+        assert np.array_equal(hist.cpu().numpy(), orc.histogram(codes))
+        seen |= {bool(v) for v in (np.abs(mi.astype(np.int64)) > 255).reshape(-1)}
+    assert seen == {True, False}                             # both kinds of unit were met
+
+
 def test_zero_scale_unit_is_flagged(ops):
     x = torch.ones(64, 1, 1, 128, dtype=torch.float16, device="cuda")
     codes, mi, sc, _, st = ops.quantize(x, 0, 64, 0.05, True)
