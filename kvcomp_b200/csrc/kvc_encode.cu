@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(ENC_THREADS, 16) encode_onepass_kernel(
     const bool fits = nbytes <= 8191u;                       // else its u16 fields cannot describe the block
     // Later blocks may add this block's bytes to their offsets from here on; its own offset is looked up
     // after the encoding, when the blocks before it have long announced theirs.
-    if (tid == 0 && blk > 0) st_state(state + blk, ST_AGG | nbytes);
+    if (tid == 0 && !(starve && blk == 0)) st_state(state + blk, (blk > 0 ? ST_AGG : ST_PREFIX) | nbytes);   // the first block's offset is 0
     if (fits) {
         // The image starts at byte 0 of the shared array, whatever the destination's alignment; it is zeroed
         // past the words the copy-out may touch.
