@@ -320,6 +320,40 @@ def test_encode_wait_between_blocks_runs_out_and_returns(ops):
     assert torch.equal(enc[:r["n"]], r["enc"][:r["n"]]) and torch.equal(bi, r["bi"]) and torch.equal(ti, r["ti"])
 
 
+def test_encode_random_shapes_books_and_alignments(ops):
+    """Random block counts, alphabets of 1 to 256 symbols (table in registers, in shared memory, codes beyond 16
+    bits), destinations at every alignment: the stream, block_info and thread_info equal the checker's and the
+    stream decodes to the codes."""
+    rng = np.random.default_rng(2024)
+    for case in range(32):
+        is_k = bool(case & 1)
+        T = int(rng.integers(1, 6)) * (64 if is_k else 128)
+        B, H = int(rng.integers(1, 4)), int(rng.integers(1, 5))
+        nsym = [1, 2, 5, 21, 32, 33, 60, 120, 256][case % 9]
+        prob = rng.random(nsym) ** (6 if case % 4 == 3 else 3) + 1e-6      # every fourth case: long codes
+        codes = rng.choice(nsym, size=(T, B, H, 128), p=prob / prob.sum()).astype(np.uint8)
+        book = ops.build_codebook(ops.histogram(dev(codes).view(-1)))
+        oenc, _ = orc.gen_codes(orc.histogram(codes))
+        odata, obi, oti, ov = orc.encode(codes, is_k, oenc)
+        bsz, tsz, _, cap = ops.buffer_sizes(T, B * H * 128, is_k)
+        bi = torch.zeros(bsz, dtype=torch.uint8, device="cuda")
+        ti = torch.zeros(tsz // 2, dtype=torch.int16, device="cuda")
+        buf = torch.zeros(cap + 16, dtype=torch.uint8, device="cuda")
+        off = case % 16
+        total, st = ops.encode(dev(codes), is_k, book.encode_table(), bi, ti, buf[off:off + cap])
+        flags = ops.read_status(st, raise_on_fatal=False)
+        assert flags & ~0x30 == 0, (case, flags)
+        if flags & 0x30:                       # a vector or block beyond what the format describes: nothing to compare
+            continue
+        n = int(total[0])
+        assert n == odata.size, case
+        assert np.array_equal(buf[off:off + n].cpu().numpy(), odata), case
+        assert np.array_equal(bi.cpu().numpy(), obi) and np.array_equal(ti.cpu().numpy().view(np.uint16), oti), case
+        assert int(buf[:off].sum()) == 0 and int(buf[off + n:].sum()) == 0, case      # nothing written outside the stream
+        out, st = ops.decode(buf[off:off + n], bi, ti, book, T, B, H, is_k, max_block=int(total[1]))
+        assert ops.read_status(st) == 0 and np.array_equal(out.cpu().numpy(), codes), case
+
+
 def test_book_from_reference_decode_tensor(ops):
     k, _, _ = synth(128, 1, 2, seed=4)
     r = _pipeline(ops, k, True, 0, 64, 0.05, True)
