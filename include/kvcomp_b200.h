@@ -231,10 +231,12 @@ int kvc_fused_pv(const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t 
  * [B,Hq,128].  Scores never leave the SM; no fp16 K/V is written to memory.
  * Work is cut into items, one (sequence, KV head) column x one of `splits` equal runs of
  * 256-token tiles; as many CTAs as the device holds at once take items until none is left,
- * and a second small kernel merges the `splits` partial results of every head.  splits = 0
+ * and a second small kernel merges the `splits` partial results of every head and adds the
+ * tail's tokens (it does the whole step when T = 0).  splits = 0
  * picks kvc_attn_splits(T, B, Hkv, 0).  workspace: kvc_attn_workspace(B, Hq, splits) bytes
  * of device memory whose first 256 bytes the caller zeroes once before the first use (the
- * kernel leaves them zeroed); NULL is allowed when splits = 1.  Launches that share a
+ * kernel leaves them zeroed); NULL is allowed when splits = 1 (a tail then costs more: the
+ * first kernel reads it itself, a column's CTA at a time).  Launches that share a
  * workspace must not overlap on the device. */
 int64_t kvc_attn_workspace(int64_t B, int64_t Hq, int splits);
 int kvc_attn_splits(int64_t T, int64_t B, int64_t Hkv, int sm_count);

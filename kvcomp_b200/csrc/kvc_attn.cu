@@ -572,6 +572,7 @@ struct AttnParams {
     float *ws_part;               // [B*Hq][splits][ATTN_PART_FLOATS]
     int *sched;                   // {items handed out, CTAs finished}, or null: static shares
     int *status;
+    int partial;                  // items leave partial results for the merge kernel (several runs per column, or a tail that the merge kernel adds)
     int wait_limit;               // tries of a staging wait before it gives up (KVC_FLAG_WAIT_TIMEOUT)
     int starve;                   // tests of the bounded waits only: announce bytes that are never copied
 };
@@ -821,8 +822,9 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
         cur = nxt;
     }
 
-    // ---- uncompressed tail (the recent window), handled with the column's last tiles: dense fp16 rows
-    if (p.Tr > 0 && it.t_hi == n_tiles) {
+    // ---- uncompressed tail (the recent window), handled with the column's last tiles: dense fp16 rows.
+    // Only for callers without a workspace: otherwise the merge kernel adds the tail (see there).
+    if (p.Tr > 0 && !p.partial && it.t_hi == n_tiles) {
         float *pt = reinterpret_cast<float *>(sm.w);           // p[row][g] for 256 rows
         for (long long r0 = 0; r0 < p.Tr; r0 += 256) {
             const long long r = r0 + tid;
@@ -885,7 +887,7 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     }
     if (it.t_lo >= it.t_hi && have_next) q_fetch(nit.col);     // an item without tiles fetched nothing yet
     const long long head0 = b * Hq + hq0;
-    if (p.splits == 1) {
+    if (!p.partial) {
         // ---- the item is the whole column: combine the CTA's two token groups and write the output
         __syncthreads();
         float *sumbuf = reinterpret_cast<float *>(sm.w);       // [2][128][G]
@@ -925,24 +927,114 @@ __global__ void __launch_bounds__(NTHR, G == 4 ? 2 : 3) attn_decode_kernel(AttnP
     }
 }
 
-// Merges the `splits` partial results of every head: grid = heads, 128 threads = channels.  The loads of the
-// partial results are issued in batches before any is used (a loop whose every load waits for the one
-// before costs a memory latency per split).
-__global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits) {
-    __shared__ float sm_red[4], sm_e[128];
+// The uncompressed tail of a cache (the recent window): dense fp16 rows [Tr, B, Hkv, 128] behind the compressed part.
+struct TailArgs {
+    const __half *q, *ktail, *vtail;
+    long long Tr;
+    int B, Hkv, Hq;
+    float scaling;
+};
+
+// Loads that stay where they are written: a batch of them is issued before the first use (left to itself the
+// compiler moves each load down to its use, and the batch becomes a chain of memory round trips).
+__device__ __forceinline__ uint4 ld_nc_128_pinned(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ unsigned short ld_nc_16_pinned(const void *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+// Merges the `splits` partial results of every head and adds the tail: grid = heads, 128 threads = channels.
+//
+// The tail is this kernel's work, not the attention kernel's: its rows lie a whole token row apart in memory, so
+// every step of it (the query, the K rows, the V rows) is a round trip to memory with little to do in between.
+// Inside the attention kernel each column's tail held a 256-thread CTA and its third of an SM for those round
+// trips (a 128-row tail lengthened a 137 us launch by 160 us when its loads depended on one another, by 25 us
+// with deep batches).  Here every head's tail is in flight at once on small CTAs, and it runs before the
+// grid-dependency wait, i.e. while the attention kernel's last CTAs still work: it reads nothing that kernel writes.
+// The loads of the partial results are issued in batches before any is used as well.
+#ifndef KVC_MT_KB
+#define KVC_MT_KB 8
+#endif
+#ifndef KVC_MT_VB
+#define KVC_MT_VB 32
+#endif
+__global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits, TailArgs t) {
+    __shared__ float sm_red[4], sm_sum[4], sm_e[128], sm_q[128];
     const float *src = ws_part + (size_t)blockIdx.x * splits * ATTN_PART_FLOATS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // launched with programmatic stream serialisation: the kernel behind this one in the stream may set up
     // while this one runs (it touches nothing this one writes before its own wait), and this one's CTAs may be
     // resident before the attention kernel has finished; its partial results are complete and visible after the wait
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    float m_t = -CUDART_INF_F, l_t = 0.f, o_t = 0.f;      // the tail's running maximum, sum and (channel tid) output
+    if (t.Tr > 0) {
+        const long long b = blockIdx.x / t.Hq, h = (blockIdx.x % t.Hq) / (t.Hq / t.Hkv);
+        const long long rstride = (long long)t.B * t.Hkv * 128;                 // halves between two rows of a column
+        const __half *kcol = t.ktail + (b * t.Hkv + h) * 128, *vcol = t.vtail + (b * t.Hkv + h) * 128 + tid;
+        sm_q[tid] = __half2float(t.q[(size_t)blockIdx.x * 128 + tid]) * t.scaling;
+        for (long long r0 = 0; r0 < t.Tr; r0 += 128) {                        // 128 rows per pass: thread = row for q.k
+            const int n_here = (int)min(128ll, t.Tr - r0);
+            const bool act = tid < n_here;
+            __syncthreads();                                                  // sm_q is written; the pass before is done with sm_e
+            float sc = -CUDART_INF_F;
+            if (act) {
+                sc = 0.f;
+                const __half *kr = kcol + (r0 + tid) * rstride;
+#pragma unroll
+                for (int c0 = 0; c0 < 16; c0 += KVC_MT_KB) {                  // the row's 16-byte loads in flight together
+                    uint4 kv[KVC_MT_KB];
+#pragma unroll
+                    for (int j = 0; j < KVC_MT_KB; j++) kv[j] = ld_nc_128_pinned(kr + (c0 + j) * 8);
+#pragma unroll
+                    for (int j = 0; j < KVC_MT_KB; j++) {
+                        const __half2 *kh = reinterpret_cast<const __half2 *>(&kv[j]);
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const float2 kf = __half22float2(kh[k]);
+                            sc = fmaf(kf.x, sm_q[(c0 + j) * 8 + 2 * k], sc);
+                            sc = fmaf(kf.y, sm_q[(c0 + j) * 8 + 2 * k + 1], sc);
+                        }
+                    }
+                }
+            }
+            const float mx = kvc_warp_max(sc);
+            if (lane == 0) sm_red[warp] = mx;
+            __syncthreads();
+            const float m_new = fmaxf(m_t, fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3])));
+            const float alpha = __expf(m_t - m_new);                          // exp(-inf) = 0 in the first pass
+            const float pr = act ? __expf(sc - m_new) : 0.f;
+            sm_e[tid] = pr;
+            const float ps = kvc_warp_sum(pr);
+            if (lane == 0) sm_sum[warp] = ps;
+            __syncthreads();
+            l_t = l_t * alpha + ((sm_sum[0] + sm_sum[1]) + (sm_sum[2] + sm_sum[3]));
+            m_t = m_new;
+            float dv = 0.f;                                                   // thread = channel: the pass's rows, many loads in flight at a time
+            const __half *vr = vcol + r0 * rstride;
+#pragma unroll 1
+            for (int i0 = 0; i0 < n_here; i0 += KVC_MT_VB) {
+                unsigned short vv[KVC_MT_VB];
+#pragma unroll
+                for (int k = 0; k < KVC_MT_VB; k++) vv[k] = ld_nc_16_pinned(vr + min(i0 + k, n_here - 1) * rstride);   // rows beyond the pass: weight 0
+#pragma unroll
+                for (int k = 0; k < KVC_MT_VB; k++) dv = fmaf(sm_e[min(i0 + k, 127)], __half2float(__ushort_as_half(vv[k])), dv);
+            }
+            o_t = fmaf(o_t, alpha, dv);
+        }
+        __syncthreads();                                                      // sm_red and sm_e serve the merge below
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     float M = -CUDART_INF_F;                              // the maximum over all partial results
     for (int s2 = tid; s2 < splits; s2 += 128) M = fmaxf(M, src[(size_t)s2 * ATTN_PART_FLOATS]);
     M = kvc_warp_max(M);
     if (lane == 0) sm_red[warp] = M;
     __syncthreads();
-    M = fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3]));
+    M = fmaxf(fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3])), m_t);
     float O = 0.f, L = 0.f;
     for (int s0 = 0; s0 < splits; s0 += 128) {
         const int ns = min(128, splits - s0);
@@ -972,6 +1064,9 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict
     if (lane == 0) sm_red[warp] = L;
     __syncthreads();
     L = (sm_red[0] + sm_red[1]) + (sm_red[2] + sm_red[3]);
+    const float e_t = m_t == -CUDART_INF_F ? 0.f : __expf(m_t - M);
+    O = fmaf(o_t, e_t, O);
+    L = fmaf(l_t, e_t, L);
     out[(size_t)blockIdx.x * 128 + tid] = __float2half_rn(O / L);
 }
 
@@ -1126,7 +1221,7 @@ constexpr int64_t ATTN_COUNTER_BYTES = 256;
 
 extern "C" int64_t kvc_attn_workspace(int64_t B, int64_t Hq, int splits) {
     if (splits < 1) splits = 1;
-    return ATTN_COUNTER_BYTES + (splits > 1 ? B * Hq * (int64_t)splits * ATTN_PART_FLOATS * 4 : 0);
+    return ATTN_COUNTER_BYTES + B * Hq * (int64_t)(splits > 1 ? splits : 1) * ATTN_PART_FLOATS * 4;    // one run still leaves a partial result when a tail follows
 }
 
 extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T, int64_t B, int64_t Hkv, int64_t Hq,
@@ -1177,6 +1272,12 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     const bool have_ws = workspace && workspace_bytes >= ATTN_COUNTER_BYTES && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
     p.sched = have_ws ? reinterpret_cast<int *>(workspace) : nullptr;
     p.ws_part = have_ws ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) + ATTN_COUNTER_BYTES) : nullptr;
+    // The tail belongs to the merge kernel whenever the attention kernel can leave partial results for it (a
+    // workspace with room for them) or has nothing to do at all (no compressed part); only a caller without a
+    // workspace gets the tail from the attention kernel itself.
+    const bool ws_parts = have_ws && workspace_bytes >= kvc_attn_workspace(B, Hq, splits);
+    const bool tail_in_merge = Tr > 0 && (T == 0 || splits > 1 || ws_parts);
+    p.partial = splits > 1 || (tail_in_merge && T > 0);
     p.status = status;
     p.wait_limit = g_wait_limit > 0 ? g_wait_limit : KVC_WAIT_LIMIT;
     p.starve = g_starve;
@@ -1189,7 +1290,7 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
     const bool bulk = T > 0 && (reinterpret_cast<uintptr_t>(k->encoded) & 15) == 0 && (reinterpret_cast<uintptr_t>(v->encoded) & 15) == 0;
     const int sms = kvc_sm_count();
     const long long Gt = Hq / Hkv;
-    for (long long g0 = 0; g0 < Gt;) {
+    for (long long g0 = 0; g0 < Gt && !(T == 0 && tail_in_merge);) {       // nothing compressed: the merge kernel alone
         const int G = next_chunk(Gt - g0);
         p.g0 = g0;
 #define KVC_AT(GG, BB)                                                                                          \
@@ -1208,9 +1309,15 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
 #undef KVC_AT
         g0 += G;
     }
-    if (splits > 1)
+    if (p.partial || tail_in_merge) {
+        TailArgs ta = {};
+        if (tail_in_merge) {
+            ta.q = p.q; ta.ktail = p.ktail; ta.vtail = p.vtail; ta.Tr = Tr;
+            ta.B = (int)B; ta.Hkv = (int)Hkv; ta.Hq = (int)Hq; ta.scaling = scaling;
+        }
         if (int rc = launch_overlapped(attn_merge_kernel, dim3((unsigned)(B * Hq)), dim3(128), 0, kvc_cu(stream),
-                                       (const float *)p.ws_part, p.out, splits)) return rc;
+                                       (const float *)p.ws_part, p.out, T > 0 ? splits : 0, ta)) return rc;
+    }
     KVC_LAUNCH_OK();
     return KVC_OK;
 }

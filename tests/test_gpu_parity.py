@@ -507,6 +507,11 @@ def test_attn_decode(ops, kmode, vmode, shared, T, B, Hkv, Hq, Tr, splits, min_d
     o1, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
     o2, _ = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=splits, workspace=ws)
     assert torch.equal(o1, o2) and torch.equal(o1, out)
+    # without any workspace (one run per column, fixed shares of the columns) the attention kernel writes the
+    # output itself and reads the tail itself; with one the merge kernel adds the tail
+    o3, st = ops.attn_decode(kc, vc, T, B, Hkv, dev(q), scaling, kt, vt, splits=1, workspace=False)
+    assert ops.read_status(st) == 0
+    assert_attn_close(o3, O)
 
 
 @pytest.mark.parametrize("B,Hkv,Hq,T,Tr", [(2, 2, 8, 1024, 0), (1, 2, 10, 768, 45), (3, 10, 40, 256, 0)])
