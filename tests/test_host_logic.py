@@ -132,7 +132,7 @@ def test_attention_run_plan_without_a_gpu():
         assert 1 <= parts <= n_tiles
         # enough items for the CTAs the device holds, unless the cache has fewer tiles than that
         assert parts * B * Hkv >= min(n_tiles * B * Hkv, 3 * sms) or parts == n_tiles
-        assert lib.kvc_attn_workspace(B, Hkv, parts) == 256 + (B * Hkv * parts * 260 * 4 if parts > 1 else 0)
+        assert lib.kvc_attn_workspace(B, Hkv, parts) == 256 + B * Hkv * parts * 260 * 4     # one run still leaves a partial result when a tail follows
     assert lib.kvc_attn_splits(4096, 8, 32, sms) == 8          # runs of 2 tiles
     assert lib.kvc_attn_splits(32768, 16, 8, sms) == 20        # 10 runs of 9 tiles, then 10 of (at most) 4
     assert lib.kvc_attn_splits(0, 8, 32, sms) == 1
