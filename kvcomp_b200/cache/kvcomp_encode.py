@@ -15,7 +15,7 @@ import torch
 
 from .. import ops
 from .._lib import KvcError
-from ..utils.compute import QuantMode, cut_tensor_ctx_len_0
+from ..utils.compute import QuantMode, cut_len, cut_tensor_ctx_len_0
 from ..utils.config import KVCompCacheConfigStatic
 
 _MODE = {QuantMode.BlockQuant: ops.MODE_BLOCK, QuantMode.ChannelQuant: ops.MODE_CHANNEL,
@@ -40,6 +40,47 @@ class _Arena:
 
     def used(self):
         return self.buf[:self.n] if self.buf is not None else None
+
+
+class _RecentRows:
+    """The uncompressed recent tokens, fp16 [r, B, H, D], kept in place: a buffer that new rows are written
+    into and whose front is released when its tokens are compressed, instead of a tensor that is concatenated
+    anew at every store (the reference's torch.cat, models/cache/kvcomp_encode.py:80: a copy of the whole
+    window, some ten megabytes per tensor and layer, at every decode step).  The live rows are moved to the
+    front only when the end of the buffer is reached."""
+
+    def __init__(self):
+        self.buf, self.lo, self.hi = None, 0, 0
+
+    def __len__(self):
+        return self.hi - self.lo
+
+    def view(self):
+        return None if self.buf is None else self.buf[self.lo:self.hi]
+
+    def release(self, n):
+        self.lo += n
+        if self.lo == self.hi:
+            self.lo = self.hi = 0
+
+    def append(self, rows, room):
+        """Add rows [t, B, H, D]; `room`: rows to leave space for beyond what is needed now."""
+        t = rows.shape[0]
+        live = self.hi - self.lo
+        if self.buf is None or self.hi + t > self.buf.shape[0]:
+            if self.buf is not None and live + t <= self.buf.shape[0] and self.lo >= live:
+                self.buf[:live] = self.buf[self.lo:self.hi]         # the two ranges do not overlap
+            else:
+                new = torch.empty((live + t + room,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+                if live:
+                    new[:live] = self.buf[self.lo:self.hi]
+                self.buf = new
+            self.lo, self.hi = 0, live
+        self.buf[self.hi:self.hi + t] = rows
+        self.hi += t
+
+    def set(self, rows):
+        self.buf, self.lo, self.hi = rows, 0, (0 if rows is None else rows.shape[0])
 
 
 class KVCompCtx:
@@ -86,7 +127,7 @@ class KVCompCtx:
         self.keep_dequantised = keep_dequantised
         self._xhat, self._xhat_start = None, 0   # fp16 values of the quantised tokens from _xhat_start on
         self.device = None
-        self.buffer = None                       # uncompressed recent tokens, fp16 [r, B, H, D]
+        self._recent = _RecentRows()             # uncompressed recent tokens, fp16 [r, B, H, D] (self.buffer)
         self.book = None
         self.max_block_bytes = 0
         self._enc = _Arena(torch.uint8)
@@ -97,6 +138,14 @@ class KVCompCtx:
         self._hist = None
 
     # ---- views with the reference's attribute names --------------------------------------------
+    @property
+    def buffer(self):
+        return self._recent.view()
+
+    @buffer.setter
+    def buffer(self, rows):
+        self._recent.set(rows)
+
     @property
     def encoded_data(self):
         return self._enc.used()
@@ -165,16 +214,28 @@ class KVCompCtx:
         Returns the uint8 codes of the newly compressed tokens as [n_blocks, block, B, H, D] (or None)."""
         self._check(cache)
         self.ctx_len += cache.shape[0]
-        to_compress, self.buffer = cut_tensor_ctx_len_0(self.buffer, cache, self.cut_block, self.recent_size)
-        if to_compress is not None and to_compress.shape[0] % self.cut_block:
-            # recent_size = 0 with a ragged length: the reference's slice clips to the length and its
-            # .view then fails (kvcomp_encode.py:83); here the ragged rest simply stays in the buffer
-            whole = to_compress.shape[0] // self.cut_block * self.cut_block
-            self.buffer = torch.cat([to_compress[whole:], self.buffer], dim=0)
-            to_compress = to_compress[:whole] if whole else None
-        if to_compress is None:
+        # utils/compute.py:59-72: the first n tokens of (recent window + new tokens) are compressed.  With
+        # recent_size = 0 and a ragged length the reference's slice clips to the length and its .view then
+        # fails (kvcomp_encode.py:83); here the ragged rest simply stays in the window.
+        live, t = len(self._recent), cache.shape[0]
+        n = min(cut_len(live + t, self.cut_block, self.recent_size), live + t) // self.cut_block * self.cut_block
+        room = self.recent_size // 2 + self.cut_block          # rows to spare when the window's buffer has to grow
+        if n == 0:
+            self._recent.append(cache, room)                  # the usual decode step: the new rows, nothing else moves
             return None
-        x = to_compress.contiguous()
+        if live == 0:
+            x = cache[:n].contiguous()                        # a prefill: compressed from where it lies
+            if n < t:
+                self._recent.append(cache[n:], room)
+        elif n <= live:
+            x = self._recent.view()[:n].clone()               # (the window's front is reused once its rows are released)
+            self._recent.release(n)
+            self._recent.append(cache, room)
+        else:
+            x = torch.cat([self._recent.view(), cache[:n - live]], dim=0)
+            self._recent.release(live)
+            if n - live < t:
+                self._recent.append(cache[n - live:], room)
         T = x.shape[0]
         hist = None
         if self.book is None:
