@@ -948,7 +948,7 @@ __device__ __forceinline__ unsigned short ld_nc_16_pinned(const void *p) {
     return v;
 }
 
-// Merges the `splits` partial results of every head and adds the tail: grid = heads, 128 threads = channels.
+// Merges the `splits` partial results of every head and adds the tail: grid = heads; 256 threads: the first 128 are the output channels.
 //
 // The tail is this kernel's work, not the attention kernel's: its rows lie a whole token row apart in memory, so
 // every step of it (the query, the K rows, the V rows) is a round trip to memory with little to do in between.
@@ -957,117 +957,138 @@ __device__ __forceinline__ unsigned short ld_nc_16_pinned(const void *p) {
 // with deep batches).  Here every head's tail is in flight at once on small CTAs, and it runs before the
 // grid-dependency wait, i.e. while the attention kernel's last CTAs still work: it reads nothing that kernel writes.
 // The loads of the partial results are issued in batches before any is used as well.
-#ifndef KVC_MT_KB
-#define KVC_MT_KB 8
-#endif
-#ifndef KVC_MT_VB
-#define KVC_MT_VB 32
-#endif
-__global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits, TailArgs t) {
-    __shared__ float sm_red[4], sm_sum[4], sm_e[128], sm_q[128];
+constexpr int MERGE_THREADS = 256;
+__global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float *__restrict__ ws_part, __half *__restrict__ out, int splits, TailArgs t) {
+    __shared__ float sm_red[8], sm_sum[8], sm_e[128], sm_o[128];
+    __shared__ __align__(16) float sm_q[128];
     const float *src = ws_part + (size_t)blockIdx.x * splits * ATTN_PART_FLOATS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // launched with programmatic stream serialisation: the kernel behind this one in the stream may set up
     // while this one runs (it touches nothing this one writes before its own wait), and this one's CTAs may be
     // resident before the attention kernel has finished; its partial results are complete and visible after the wait
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    float m_t = -CUDART_INF_F, l_t = 0.f, o_t = 0.f;      // the tail's running maximum, sum and (channel tid) output
+    float m_t = -CUDART_INF_F, l_t = 0.f, o_t = 0.f;      // the tail's running maximum and sum; output of channel tid & 127 over the thread's rows
     if (t.Tr > 0) {
+        // q.k: two threads per row, 64 channels each; P.V: thread = (half of the pass's rows, channel)
+        const int row = tid >> 1, part = tid & 1, ch = tid & 127, rg = tid >> 7;
         const long long b = blockIdx.x / t.Hq, h = (blockIdx.x % t.Hq) / (t.Hq / t.Hkv);
         const long long rstride = (long long)t.B * t.Hkv * 128;                 // halves between two rows of a column
-        const __half *kcol = t.ktail + (b * t.Hkv + h) * 128, *vcol = t.vtail + (b * t.Hkv + h) * 128 + tid;
-        sm_q[tid] = __half2float(t.q[(size_t)blockIdx.x * 128 + tid]) * t.scaling;
-        for (long long r0 = 0; r0 < t.Tr; r0 += 128) {                        // 128 rows per pass: thread = row for q.k
+        const __half *kcol = t.ktail + (b * t.Hkv + h) * 128 + part * 64, *vcol = t.vtail + (b * t.Hkv + h) * 128 + ch;
+        if (tid < 128) sm_q[tid] = __half2float(t.q[(size_t)blockIdx.x * 128 + tid]) * t.scaling;
+        for (long long r0 = 0; r0 < t.Tr; r0 += 128) {                        // 128 rows per pass
             const int n_here = (int)min(128ll, t.Tr - r0);
-            const bool act = tid < n_here;
+            const bool act = row < n_here;
             __syncthreads();                                                  // sm_q is written; the pass before is done with sm_e
             float sc = -CUDART_INF_F;
             if (act) {
-                sc = 0.f;
-                const __half *kr = kcol + (r0 + tid) * rstride;
+                const __half *kr = kcol + (r0 + row) * rstride;
+                uint4 kv[8];                                                  // the thread's eight 16-byte loads in flight together
 #pragma unroll
-                for (int c0 = 0; c0 < 16; c0 += KVC_MT_KB) {                  // the row's 16-byte loads in flight together
-                    uint4 kv[KVC_MT_KB];
+                for (int j = 0; j < 8; j++) kv[j] = ld_nc_128_pinned(kr + j * 8);
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;                 // four sums: no chain of 64 dependent additions
 #pragma unroll
-                    for (int j = 0; j < KVC_MT_KB; j++) kv[j] = ld_nc_128_pinned(kr + (c0 + j) * 8);
-#pragma unroll
-                    for (int j = 0; j < KVC_MT_KB; j++) {
-                        const __half2 *kh = reinterpret_cast<const __half2 *>(&kv[j]);
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            const float2 kf = __half22float2(kh[k]);
-                            sc = fmaf(kf.x, sm_q[(c0 + j) * 8 + 2 * k], sc);
-                            sc = fmaf(kf.y, sm_q[(c0 + j) * 8 + 2 * k + 1], sc);
-                        }
-                    }
+                for (int j = 0; j < 8; j++) {
+                    const __half2 *kh = reinterpret_cast<const __half2 *>(&kv[j]);
+                    const float4 q0 = *reinterpret_cast<const float4 *>(&sm_q[part * 64 + j * 8]);
+                    const float4 q1 = *reinterpret_cast<const float4 *>(&sm_q[part * 64 + j * 8 + 4]);
+                    const float2 k0 = __half22float2(kh[0]), k1 = __half22float2(kh[1]), k2 = __half22float2(kh[2]), k3 = __half22float2(kh[3]);
+                    a0 = fmaf(k0.x, q0.x, a0); a1 = fmaf(k0.y, q0.y, a1); a2 = fmaf(k1.x, q0.z, a2); a3 = fmaf(k1.y, q0.w, a3);
+                    a0 = fmaf(k2.x, q1.x, a0); a1 = fmaf(k2.y, q1.y, a1); a2 = fmaf(k3.x, q1.z, a2); a3 = fmaf(k3.y, q1.w, a3);
                 }
+                sc = (a0 + a1) + (a2 + a3);
             }
+            const float other = __shfl_xor_sync(0xffffffffu, sc, 1);          // the row's other half (both -inf beyond the tail)
+            sc = act ? sc + other : sc;
             const float mx = kvc_warp_max(sc);
             if (lane == 0) sm_red[warp] = mx;
             __syncthreads();
-            const float m_new = fmaxf(m_t, fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3])));
+            float mt = sm_red[0];
+#pragma unroll
+            for (int w = 1; w < 8; w++) mt = fmaxf(mt, sm_red[w]);
+            const float m_new = fmaxf(m_t, mt);
             const float alpha = __expf(m_t - m_new);                          // exp(-inf) = 0 in the first pass
             const float pr = act ? __expf(sc - m_new) : 0.f;
-            sm_e[tid] = pr;
-            const float ps = kvc_warp_sum(pr);
+            if (part == 0) sm_e[row] = pr;
+            const float ps = kvc_warp_sum(part == 0 ? pr : 0.f);
             if (lane == 0) sm_sum[warp] = ps;
             __syncthreads();
-            l_t = l_t * alpha + ((sm_sum[0] + sm_sum[1]) + (sm_sum[2] + sm_sum[3]));
+            float lsum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) lsum += sm_sum[w];
+            l_t = l_t * alpha + lsum;
             m_t = m_new;
-            float dv = 0.f;                                                   // thread = channel: the pass's rows, many loads in flight at a time
+            // rows rg * 64 .. + 63 of the pass, 32 loads in flight at a time, four sums
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
             const __half *vr = vcol + r0 * rstride;
 #pragma unroll 1
-            for (int i0 = 0; i0 < n_here; i0 += KVC_MT_VB) {
-                unsigned short vv[KVC_MT_VB];
+            for (int i0 = rg * 64; i0 < min(n_here, rg * 64 + 64); i0 += 32) {
+                unsigned short vv[32];
 #pragma unroll
-                for (int k = 0; k < KVC_MT_VB; k++) vv[k] = ld_nc_16_pinned(vr + min(i0 + k, n_here - 1) * rstride);   // rows beyond the pass: weight 0
+                for (int k = 0; k < 32; k++) vv[k] = ld_nc_16_pinned(vr + min(i0 + k, n_here - 1) * rstride);   // rows beyond the pass: weight 0
 #pragma unroll
-                for (int k = 0; k < KVC_MT_VB; k++) dv = fmaf(sm_e[min(i0 + k, 127)], __half2float(__ushort_as_half(vv[k])), dv);
+                for (int k = 0; k < 32; k += 4) {
+                    d0 = fmaf(sm_e[min(i0 + k, 127)], __half2float(__ushort_as_half(vv[k])), d0);
+                    d1 = fmaf(sm_e[min(i0 + k + 1, 127)], __half2float(__ushort_as_half(vv[k + 1])), d1);
+                    d2 = fmaf(sm_e[min(i0 + k + 2, 127)], __half2float(__ushort_as_half(vv[k + 2])), d2);
+                    d3 = fmaf(sm_e[min(i0 + k + 3, 127)], __half2float(__ushort_as_half(vv[k + 3])), d3);
+                }
             }
-            o_t = fmaf(o_t, alpha, dv);
+            o_t = fmaf(o_t, alpha, (d0 + d1) + (d2 + d3));
         }
         __syncthreads();                                                      // sm_red and sm_e serve the merge below
+        if (tid >= 128) sm_o[tid - 128] = o_t;                                // the second half of the rows joins the first
+        __syncthreads();
+        if (tid < 128) o_t += sm_o[tid];
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     float M = -CUDART_INF_F;                              // the maximum over all partial results
-    for (int s2 = tid; s2 < splits; s2 += 128) M = fmaxf(M, src[(size_t)s2 * ATTN_PART_FLOATS]);
+    for (int s2 = tid; s2 < splits; s2 += MERGE_THREADS) M = fmaxf(M, src[(size_t)s2 * ATTN_PART_FLOATS]);
     M = kvc_warp_max(M);
     if (lane == 0) sm_red[warp] = M;
     __syncthreads();
-    M = fmaxf(fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3])), m_t);
-    float O = 0.f, L = 0.f;
+    M = m_t;
+#pragma unroll
+    for (int w = 0; w < 8; w++) M = fmaxf(M, sm_red[w]);
+    float O = 0.f, L = 0.f;                               // O: channel tid of threads 0..127 (the others idle along)
+    const int c = tid & 127;
     for (int s0 = 0; s0 < splits; s0 += 128) {
         const int ns = min(128, splits - s0);
         __syncthreads();                                  // the weights of the batch before are spent
-        float e = 0.f;
-        if (tid < ns) {
-            const float *pp = src + (size_t)(s0 + tid) * ATTN_PART_FLOATS;
-            const float m2 = pp[0];
-            e = m2 == -CUDART_INF_F ? 0.f : __expf(m2 - M);
-            L = fmaf(pp[1], e, L);
-        }
-        sm_e[tid] = e;
-        __syncthreads();
-        for (int i0 = 0; i0 < ns; i0 += 8) {              // channel tid of 8 partial results, all loads in flight together
-            float a[8];
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
-                const float *pp = src + (size_t)(s0 + min(i0 + k, ns - 1)) * ATTN_PART_FLOATS;
-                a[k] = pp[4 + tid] + pp[4 + 128 + tid];
+        if (tid < 128) {
+            float e = 0.f;
+            if (tid < ns) {
+                const float *pp = src + (size_t)(s0 + tid) * ATTN_PART_FLOATS;
+                const float m2 = pp[0];
+                e = m2 == -CUDART_INF_F ? 0.f : __expf(m2 - M);
+                L = fmaf(pp[1], e, L);
             }
+            sm_e[tid] = e;
+        }
+        __syncthreads();
+        if (tid < 128) {
+            for (int i0 = 0; i0 < ns; i0 += 8) {          // channel c of 8 partial results, all loads in flight together
+                float a[8];
 #pragma unroll
-            for (int k = 0; k < 8; k++) if (i0 + k < ns) O = fmaf(a[k], sm_e[i0 + k], O);
+                for (int k = 0; k < 8; k++) {
+                    const float *pp = src + (size_t)(s0 + min(i0 + k, ns - 1)) * ATTN_PART_FLOATS;
+                    a[k] = pp[4 + c] + pp[4 + 128 + c];
+                }
+#pragma unroll
+                for (int k = 0; k < 8; k++) if (i0 + k < ns) O = fmaf(a[k], sm_e[i0 + k], O);
+            }
         }
     }
     L = kvc_warp_sum(L);
     __syncthreads();
     if (lane == 0) sm_red[warp] = L;
     __syncthreads();
-    L = (sm_red[0] + sm_red[1]) + (sm_red[2] + sm_red[3]);
+    L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) L += sm_red[w];           // warps 0..3 hold the partial results' sums
     const float e_t = m_t == -CUDART_INF_F ? 0.f : __expf(m_t - M);
     O = fmaf(o_t, e_t, O);
     L = fmaf(l_t, e_t, L);
-    out[(size_t)blockIdx.x * 128 + tid] = __float2half_rn(O / L);
+    if (tid < 128) out[(size_t)blockIdx.x * 128 + tid] = __float2half_rn(O / L);
 }
 
 // Launch with programmatic stream serialisation: the grid may be set up on the device while the kernel
@@ -1315,7 +1336,7 @@ extern "C" int kvc_attn_decode(const kvc_cache *k, const kvc_cache *v, int64_t T
             ta.q = p.q; ta.ktail = p.ktail; ta.vtail = p.vtail; ta.Tr = Tr;
             ta.B = (int)B; ta.Hkv = (int)Hkv; ta.Hq = (int)Hq; ta.scaling = scaling;
         }
-        if (int rc = launch_overlapped(attn_merge_kernel, dim3((unsigned)(B * Hq)), dim3(128), 0, kvc_cu(stream),
+        if (int rc = launch_overlapped(attn_merge_kernel, dim3((unsigned)(B * Hq)), dim3(MERGE_THREADS), 0, kvc_cu(stream),
                                        (const float *)p.ws_part, p.out, T > 0 ? splits : 0, ta)) return rc;
     }
     KVC_LAUNCH_OK();
