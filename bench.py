@@ -472,7 +472,38 @@ def side_workloads(ops, torch, device, seed, names=("c2", "c3"), layers=2):
                      "bits_per_symbol": {k: float(np.mean([8.0 * b[3][k]["encoded"] / b[3][k]["symbols"] for b in built])) for k in ("k", "v")}}
         del built, ws, outs
         torch.cuda.empty_cache()
+    out["c1_recent_window"] = recent_window_record(ops, torch, device, seed)
     return out
+
+
+def recent_window_record(ops, torch, device, seed, layers=4, recent=128):
+    """c1's 4096-token context as a cache class holds it during decoding: the newest `recent` tokens
+    (models/cache/kvcomp_encode.py:80, k_recent_size) uncompressed as fp16 rows behind 4096 - recent compressed
+    ones.  Per-layer time of the same launch pair as the headline."""
+    from kvcomp_b200.synth import make_kv
+    cfg = dict(WORKLOADS["c1"]); cfg["T"] = WORKLOADS["c1"]["T"] - recent
+    T, B, Hkv, Hq = cfg["T"], cfg["B"], cfg["Hkv"], cfg["Hq"]
+    built = [build_layer(ops, torch, cfg, l, seed, device) for l in range(layers)]
+    tails = [make_kv(recent, B, Hkv, 128, seed=seed + 17, layer=l, device=device)[:2] for l in range(layers)]
+    ws = ops.attn_workspace(B, Hq, ops.attn_splits(T, B, Hkv), device)
+    status = ops.new_status(device)
+    outs = torch.empty((layers, B, Hq, 128), dtype=torch.float16, device=device)
+    scaling = 1.0 / math.sqrt(128)
+
+    def step():
+        for i, (caches, _, q, _) in enumerate(built):
+            ops.attn_decode(caches[0], caches[1], T, B, Hkv, q, scaling, tails[i][0], tails[i][1], out=outs[i], workspace=ws, status=status)
+    for _ in range(3):
+        step()
+    blocks = timed_blocks(torch, step, 5, torch.cuda.synchronize, min_seconds=0.2)
+    ops.read_status(status, what="attn_decode")
+    ms_layer = float(np.median(blocks)) / 5 / layers
+    rec = {"workload": "c1 with the newest %d of its 4096 tokens as uncompressed fp16 rows (the recent window)" % recent,
+           "layers_timed": layers, "compressed_tokens": T, "fp16_tail_tokens": recent, "ms_per_layer": ms_layer,
+           "tokens_per_s_full_model": B / (ms_layer * WORKLOADS["c1"]["layers"] / 1e3)}
+    del built, tails, ws, outs
+    torch.cuda.empty_cache()
+    return rec
 
 
 def timed_blocks(torch, step, steps, barrier, min_seconds=MIN_TIMED_SECONDS, max_blocks=MAX_BLOCKS, world_reduce=None):

@@ -155,7 +155,8 @@ int kvc_quantize_ranged(const void *x, int64_t T, int64_t B, int64_t H, int64_t 
  * utils/compute.py:25-33: t * cos + rotate_half(t) * sin, each op rounded to fp16) fused with the
  * transposition into the cache's token-major layout: x device fp16 [B, H, t, D] (as the attention layer
  * hands it over) -> out device fp16 [t, B, H, D].  cos / sin: device fp16 [B, t, D], or [1, t, D] with
- * cos_batch_stride = 0.  Same bits as the torch ops. */
+ * cos_batch_stride = 0.  Same bits as the torch ops.  cos_ = sin_ = NULL: no rotation, the transposition
+ * alone (how new values reach the token-major recent window).  out may be a row range of a larger buffer. */
 int kvc_rope_store(const void *x, const void *cos_, const void *sin_, void *out, int64_t B, int64_t H, int64_t t,
                    int64_t D, int64_t cos_batch_stride, kvc_stream_t stream);
 

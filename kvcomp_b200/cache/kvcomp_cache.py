@@ -74,7 +74,14 @@ class KVCompCache(_BASE):
             self.sins[layer_idx] = safe_cat(self.sins[layer_idx], sin, dim=1)
         elif cfg.enable_quant and key_states.is_cuda and key_states.dtype == torch.float16 and key_states.is_contiguous() \
                 and cos.dtype == torch.float16 and key_states.shape[3] % 16 == 0:
-            k_rows = ops.rope_store(key_states, cos, sin)      # rotation and transposition in one pass, torch's bits
+            kc0 = self._ctx(layer_idx, key_states.shape[1])[0]
+            place = kc0.recent_place(key_states.shape[2], key_states.device)
+            if place is not None:                               # the usual decode step: straight into the recent window
+                ops.rope_store(key_states, cos, sin, out=place)
+                kc0.recent_commit(key_states.shape[2])
+                k_rows = False                                  # stored already
+            else:
+                k_rows = ops.rope_store(key_states, cos, sin)  # rotation and transposition in one pass, torch's bits
         else:
             key_states = apply_rotary_pos_emb_single(key_states, cos, sin)
         if not cfg.enable_quant:
@@ -82,8 +89,17 @@ class KVCompCache(_BASE):
             self.v_plain[layer_idx] = safe_cat(self.v_plain[layer_idx], value_states, dim=2)
             return
         kc, vc = self._ctx(layer_idx, key_states.shape[1])
-        kc.store(k_rows if k_rows is not None else key_states.permute(2, 0, 1, 3).contiguous().half())
-        vc.store(value_states.permute(2, 0, 1, 3).contiguous().half())
+        if k_rows is not False:
+            kc.store(k_rows if k_rows is not None else key_states.permute(2, 0, 1, 3).contiguous().half())
+        t = value_states.shape[2]
+        place = None
+        if value_states.is_cuda and value_states.dtype == torch.float16 and value_states.is_contiguous() and value_states.shape[3] % 16 == 0:
+            place = vc.recent_place(t, value_states.device)
+        if place is not None:                                   # the transposition writes straight into the window
+            ops.rope_store(value_states, None, None, out=place)
+            vc.recent_commit(t)
+        else:
+            vc.store(value_states.permute(2, 0, 1, 3).contiguous().half())
 
     def update(self, key_states, value_states, layer_idx, cache_kwargs=None):
         """The reference's Cache.update: append, then return the whole K and V as [B, Hkv, T, D]."""

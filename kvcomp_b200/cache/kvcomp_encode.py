@@ -43,44 +43,79 @@ class _Arena:
 
 
 class _RecentRows:
-    """The uncompressed recent tokens, fp16 [r, B, H, D], kept in place: a buffer that new rows are written
-    into and whose front is released when its tokens are compressed, instead of a tensor that is concatenated
-    anew at every store (the reference's torch.cat, models/cache/kvcomp_encode.py:80: a copy of the whole
-    window, some ten megabytes per tensor and layer, at every decode step).  The live rows are moved to the
-    front only when the end of the buffer is reached."""
+    """The rows behind the compressed stream, fp16 [r, B, H, D], kept in place in one buffer:
+
+        [ kept | recent )      kept:   dequantised values of quantised tokens that a reader still wants as rows
+                               recent: the uncompressed recent window (the reference's `buffer`)
+
+    New rows are written behind the recent ones; when the front of the window is compressed its rows are
+    overwritten with their dequantised values and join the kept ones (or are given up), so that both parts
+    always form one contiguous range and nothing is concatenated at a decode step (the reference's
+    torch.cat, models/cache/kvcomp_encode.py:80, copies the whole window, some ten megabytes per tensor and
+    layer, at every store).  The rows move to the front only when the end of the buffer is reached."""
 
     def __init__(self):
-        self.buf, self.lo, self.hi = None, 0, 0
+        self.buf, self.q, self.lo, self.hi = None, 0, 0, 0
 
-    def __len__(self):
+    def __len__(self):                      # recent rows
         return self.hi - self.lo
+
+    @property
+    def kept(self):
+        return self.lo - self.q
 
     def view(self):
         return None if self.buf is None else self.buf[self.lo:self.hi]
 
-    def release(self, n):
+    def rows_from_kept(self, k):
+        """The last k kept rows followed by the recent ones; earlier kept rows are given up."""
+        self.q = self.lo - k
+        if self.q == self.hi:
+            self.q = self.lo = self.hi = 0
+            return None
+        return self.buf[self.q:self.hi]
+
+    def consume(self, n):
+        """The first n recent rows were compressed: their places now belong to the kept rows."""
         self.lo += n
-        if self.lo == self.hi:
-            self.lo = self.hi = 0
+
+    def reserve(self, t, room, shape, dtype, device):
+        """Room for t more rows; returns the rows' place [t, B, H, D] without making them live (commit does)."""
+        held = self.hi - self.q
+        if self.buf is None or self.hi + t > self.buf.shape[0]:
+            if self.buf is not None and held + t <= self.buf.shape[0] and self.q >= held:
+                self.buf[:held] = self.buf[self.q:self.hi]          # the two ranges do not overlap
+            else:
+                new = torch.empty((held + t + room,) + tuple(shape), dtype=dtype, device=device)
+                if held:
+                    new[:held] = self.buf[self.q:self.hi]
+                self.buf = new
+            self.lo, self.hi, self.q = self.lo - self.q, held, 0
+        return self.buf[self.hi:self.hi + t]
+
+    def commit(self, t):
+        self.hi += t
 
     def append(self, rows, room):
         """Add rows [t, B, H, D]; `room`: rows to leave space for beyond what is needed now."""
         t = rows.shape[0]
-        live = self.hi - self.lo
-        if self.buf is None or self.hi + t > self.buf.shape[0]:
-            if self.buf is not None and live + t <= self.buf.shape[0] and self.lo >= live:
-                self.buf[:live] = self.buf[self.lo:self.hi]         # the two ranges do not overlap
-            else:
-                new = torch.empty((live + t + room,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
-                if live:
-                    new[:live] = self.buf[self.lo:self.hi]
-                self.buf = new
-            self.lo, self.hi = 0, live
-        self.buf[self.hi:self.hi + t] = rows
-        self.hi += t
+        self.reserve(t, room, rows.shape[1:], rows.dtype, rows.device)[:] = rows
+        self.commit(t)
+
+    def rebuild(self, kept, recent, room):
+        """Start over with the given kept rows and recent rows (either may be None)."""
+        parts = [p for p in (kept, recent) if p is not None and p.shape[0]]
+        nk = 0 if kept is None else kept.shape[0]
+        if not parts:
+            self.q = self.lo = self.hi = 0
+            return
+        n = sum(p.shape[0] for p in parts)
+        self.buf = torch.empty((n + room,) + tuple(parts[0].shape[1:]), dtype=parts[0].dtype, device=parts[0].device)
+        torch.cat(parts, dim=0, out=self.buf[:n])
+        self.q, self.lo, self.hi = 0, nk, n
 
     def set(self, rows):
-        self.buf, self.lo, self.hi = rows, 0, (0 if rows is None else rows.shape[0])
+        self.buf, self.q, self.lo, self.hi = rows, 0, 0, (0 if rows is None else rows.shape[0])
 
 
 class KVCompCtx:
@@ -125,7 +160,6 @@ class KVCompCtx:
         self.encoded_ctx_len = 0                 # of those, the tokens in the stream (whole Huffman blocks)
         self._pending = None                     # codes of quantised tokens whose Huffman block is not full yet
         self.keep_dequantised = keep_dequantised
-        self._xhat, self._xhat_start = None, 0   # fp16 values of the quantised tokens from _xhat_start on
         self.device = None
         self._recent = _RecentRows()             # uncompressed recent tokens, fp16 [r, B, H, D] (self.buffer)
         self.book = None
@@ -191,6 +225,23 @@ class KVCompCtx:
         return torch.Size([self.compressed_ctx_len, self.batch_size, self.head_num, self.head_dim])
 
     # ---- store ------------------------------------------------------------------------------------
+    def _room(self):
+        return self.recent_size // 2 + self.cut_block          # rows to spare when the window's buffer has to grow
+
+    def recent_place(self, t, device):
+        """Where the next t tokens would lie in the recent window, fp16 [t, B, H, D], when storing them compresses
+        nothing (the usual decode step), else None.  A caller that can produce the rows there (the rotation and
+        transposition kernel) does so and calls recent_commit(t) instead of store(rows)."""
+        if self.device is None:
+            self.device = device
+        if self.device != device or cut_len(len(self._recent) + t, self.cut_block, self.recent_size) // self.cut_block * self.cut_block:
+            return None
+        return self._recent.reserve(t, self._room(), (self.batch_size, self.head_num, self.head_dim), torch.float16, device)
+
+    def recent_commit(self, t):
+        self._recent.commit(t)
+        self.ctx_len += t
+
     def _check(self, cache):
         assert cache.dtype == torch.float16, "cache must be float16"
         assert cache.shape[1] == self.batch_size, "batch size mismatch"
@@ -219,23 +270,16 @@ class KVCompCtx:
         # fails (kvcomp_encode.py:83); here the ragged rest simply stays in the window.
         live, t = len(self._recent), cache.shape[0]
         n = min(cut_len(live + t, self.cut_block, self.recent_size), live + t) // self.cut_block * self.cut_block
-        room = self.recent_size // 2 + self.cut_block          # rows to spare when the window's buffer has to grow
+        room = self._room()
         if n == 0:
             self._recent.append(cache, room)                  # the usual decode step: the new rows, nothing else moves
             return None
         if live == 0:
-            x = cache[:n].contiguous()                        # a prefill: compressed from where it lies
-            if n < t:
-                self._recent.append(cache[n:], room)
+            x, rest = cache[:n].contiguous(), cache[n:]       # a prefill: compressed from where it lies
         elif n <= live:
-            x = self._recent.view()[:n].clone()               # (the window's front is reused once its rows are released)
-            self._recent.release(n)
-            self._recent.append(cache, room)
+            x, rest = self._recent.view()[:n].clone(), cache  # the window's front
         else:
-            x = torch.cat([self._recent.view(), cache[:n - live]], dim=0)
-            self._recent.release(live)
-            if n - live < t:
-                self._recent.append(cache[n - live:], room)
+            x, rest = torch.cat([self._recent.view(), cache[:n - live]], dim=0), cache[n - live:]
         T = x.shape[0]
         hist = None
         if self.book is None:
@@ -251,11 +295,28 @@ class KVCompCtx:
                 raise KvcError("a min_int does not fit 16 bits: the data lies too far from zero for its range")
             import warnings
             warnings.warn("a min_int wrapped in int8 as in the reference's CUDA path; set wide_min_ints to keep it")
-        if self.keep_dequantised:
-            mi = self._mi.buf[self._mi.n:self._mi.n + n_units]
-            sc = self._sc.buf[self._sc.n:self._sc.n + n_units]
-            xh = ops.dequant(codes, mi, sc, self.spec)
-            self._xhat = xh if self._xhat is None else torch.cat([self._xhat, xh], dim=0)
+        # the window: the compressed rows leave it, or stay as dequantised rows for a reader of the rows behind
+        # the fused kernel's range (tail_from); the rest of the new tokens joins the recent rows
+        mi = self._mi.buf[self._mi.n:self._mi.n + n_units]
+        sc = self._sc.buf[self._sc.n:self._sc.n + n_units]
+        if 0 < live and n <= live:
+            if self.keep_dequantised:
+                ops.dequant(codes, mi, sc, self.spec, out=self._recent.view()[:n])     # in place of the rows themselves
+                self._recent.consume(n)
+            else:
+                self._recent.consume(n)
+                self._recent.rows_from_kept(0)
+            if rest.shape[0]:
+                self._recent.append(rest, room)
+        else:
+            kept = None
+            if self.keep_dequantised:
+                k = min(n, self.KEEP_ROWS)                    # a long prefill keeps its last rows only
+                xh = ops.dequant(codes, mi, sc, self.spec)[n - k:]
+                old = self._recent.rows_from_kept(self._recent.kept if k == n else 0)
+                old = None if old is None else old[:self._recent.kept]
+                kept = xh if old is None or not old.shape[0] else torch.cat([old, xh], dim=0)
+            self._recent.rebuild(kept, rest if rest.shape[0] else None, room)
         self._mi.n += n_units
         self._sc.n += n_units
         self.compressed_ctx_len += T
@@ -440,28 +501,21 @@ class KVCompCtx:
         return original / (compressed + pending)
 
     # ---- the tokens behind the fused kernel's range ---------------------------------------------------
+    KEEP_ROWS = 512       # dequantised rows a long store keeps at most (tail_from decodes when it needs more)
+
     def tail_from(self, T):
         """fp16 [n, B, H, D]: the quantised tokens from index T on (dequantised) followed by the recent
-        window.  Needs keep_dequantised; tokens before T are dropped from the kept values."""
-        parts = []
-        if self.compressed_ctx_len > T:
-            if not self.keep_dequantised or self._xhat is None or self._xhat_start > T:
-                x, _ = self.get_only_compressed()                 # decodes the whole stream: the slow way
-                parts.append(x[T:])
-            else:
-                self.trim_dequantised(T)
-                parts.append(self._xhat)
-        elif self.keep_dequantised:
-            self.trim_dequantised(T)
-        if self.buffer is not None and self.buffer.shape[0]:
-            parts.append(self.buffer)
-        if not parts:
-            return None
-        return parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+        window, as one range of the window's buffer.  Dequantised rows before T are given up."""
+        need = max(0, self.compressed_ctx_len - T)
+        if need > self._recent.kept:
+            # not kept (keep_dequantised off, a cache read from a file, a prefill longer than KEEP_ROWS whose
+            # other tensor lags far behind): decode the stream once, keep the rows from T on
+            x, _ = self.get_only_compressed()
+            kept = x[T:].contiguous()
+            if not self.keep_dequantised:
+                return kept if not len(self._recent) else torch.cat([kept, self._recent.view()], dim=0)
+            self._recent.rebuild(kept, self._recent.view(), self._room())
+        return self._recent.rows_from_kept(need)
 
     def trim_dequantised(self, T):
-        T = min(T, self.compressed_ctx_len)
-        if self._xhat is not None and T > self._xhat_start:
-            self._xhat = self._xhat[T - self._xhat_start:] if T < self.compressed_ctx_len else None
-        if self._xhat is None or T > self._xhat_start:
-            self._xhat_start = T
+        self._recent.rows_from_kept(min(self._recent.kept, max(0, self.compressed_ctx_len - T)))

@@ -602,9 +602,14 @@ __global__ void __launch_bounds__(256) rope_store_kernel(const __half *__restric
     const int c0 = (int)(i % per_row) * 8, half = D / 2;
     const long long row = i / per_row, h = row % H, b = (row / H) % B, tok = row / (H * B);
     const __half *xr = x + ((b * H + h) * t + tok) * D;
-    const __half *cr = cs + b * cs_bstride + tok * D, *sr = sn + b * cs_bstride + tok * D;
     __half *orow = out + ((tok * B + b) * H + h) * D;
     const uint4 xa = *reinterpret_cast<const uint4 *>(xr + c0), xb = *reinterpret_cast<const uint4 *>(xr + c0 + half);
+    if (cs == nullptr) {                                         // no rotation (values): the transposition alone
+        *reinterpret_cast<uint4 *>(orow + c0) = xa;
+        *reinterpret_cast<uint4 *>(orow + c0 + half) = xb;
+        return;
+    }
+    const __half *cr = cs + b * cs_bstride + tok * D, *sr = sn + b * cs_bstride + tok * D;
     const uint4 ca = *reinterpret_cast<const uint4 *>(cr + c0), cb = *reinterpret_cast<const uint4 *>(cr + c0 + half);
     const uint4 sa = *reinterpret_cast<const uint4 *>(sr + c0), sb = *reinterpret_cast<const uint4 *>(sr + c0 + half);
     const __half *x1 = reinterpret_cast<const __half *>(&xa), *x2 = reinterpret_cast<const __half *>(&xb);
@@ -625,7 +630,7 @@ __global__ void __launch_bounds__(256) rope_store_kernel(const __half *__restric
 
 extern "C" int kvc_rope_store(const void *x, const void *cos_, const void *sin_, void *out, int64_t B, int64_t H, int64_t t,
                               int64_t D, int64_t cos_batch_stride, kvc_stream_t stream) {
-    KVC_REQUIRE(x && cos_ && sin_ && out, "kvc_rope_store: null pointer");
+    KVC_REQUIRE(x && out && ((cos_ == nullptr) == (sin_ == nullptr)), "kvc_rope_store: null pointer");
     KVC_REQUIRE(B > 0 && H > 0 && t >= 0 && D > 0 && D % 16 == 0, "kvc_rope_store: bad shape");
     KVC_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(cos_) | reinterpret_cast<uintptr_t>(sin_) |
                   reinterpret_cast<uintptr_t>(out)) & 15) == 0, "kvc_rope_store: pointers must be 16-byte aligned");

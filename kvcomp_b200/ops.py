@@ -159,17 +159,22 @@ def quantize_ranged(x, mode, block, rel, mn, mx, batch_shared=True, min_dtype=to
 
 def rope_store(x, cos, sin, out=None):
     """New keys x fp16 [B, H, t, D] rotated (t * cos + rotate_half(t) * sin in fp16, as torch evaluates it) and
-    laid out token-major: fp16 [t, B, H, D].  cos / sin: fp16 [B, t, D] or [1, t, D]."""
+    laid out token-major: fp16 [t, B, H, D].  cos / sin: fp16 [B, t, D] or [1, t, D]; both None: no rotation,
+    the transposition alone (new values).  out: where the rows go (a row range of the recent window)."""
     lib = _lib.load()
     _cuda(x, torch.float16, "key_states")
     B, H, t, D = x.shape
-    cos, sin = _cuda(cos.contiguous(), torch.float16, "cos"), _cuda(sin.contiguous(), torch.float16, "sin")
-    if cos.shape != sin.shape or cos.dim() != 3 or cos.shape[1:] != (t, D) or cos.shape[0] not in (1, B):
-        raise KvcError("cos / sin must be [B, t, D] or [1, t, D], got %s" % (tuple(cos.shape),))
+    stride = 0
+    if cos is not None:
+        cos, sin = _cuda(cos.contiguous(), torch.float16, "cos"), _cuda(sin.contiguous(), torch.float16, "sin")
+        if cos.shape != sin.shape or cos.dim() != 3 or cos.shape[1:] != (t, D) or cos.shape[0] not in (1, B):
+            raise KvcError("cos / sin must be [B, t, D] or [1, t, D], got %s" % (tuple(cos.shape),))
+        stride = 0 if cos.shape[0] == 1 and B > 1 else t * D
     out = torch.empty((t, B, H, D), dtype=torch.float16, device=x.device) if out is None else _cuda(out, torch.float16, "out")
+    if tuple(out.shape) != (t, B, H, D):
+        raise KvcError("out must be [t, B, H, D] = %s, got %s" % ((t, B, H, D), tuple(out.shape)))
     with torch.cuda.device(x.device):
-        _lib.check(lib.kvc_rope_store(_p(x), _p(cos), _p(sin), _p(out), B, H, t, D, 0 if cos.shape[0] == 1 and B > 1 else t * D,
-                                      _stream()), "kvc_rope_store")
+        _lib.check(lib.kvc_rope_store(_p(x), _p(cos), _p(sin), _p(out), B, H, t, D, stride, _stream()), "kvc_rope_store")
     return out
 
 
