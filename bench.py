@@ -473,7 +473,59 @@ def side_workloads(ops, torch, device, seed, names=("c2", "c3"), layers=2):
         del built, ws, outs
         torch.cuda.empty_cache()
     out["c1_recent_window"] = recent_window_record(ops, torch, device, seed)
+    out["c1_cache_class_loop"] = cache_class_loop_record(torch, device, seed)
     return out
+
+
+def cache_class_loop_record(torch, device, seed, layers=8, steps=96):
+    """A decode loop through the cache class the model files call (KVCompCache.append + attend per layer:
+    models/llama.py:279-283 with the fused branch), c1's shape: a 4096-token prefill, then one token per step.
+    Per-layer time including the rotation and transposition of the new token into the recent window, the
+    compression of a block whenever the window overflows (every 64 / 128 steps), and the fused attention with
+    the window as fp16 tail."""
+    from kvcomp_b200.cache import KVCompCache
+    from kvcomp_b200.synth import make_kv
+    from kvcomp_b200.utils.compute import QuantMode
+    from kvcomp_b200.utils.config import KVCompCacheConfig, KVCompCacheConfigStatic
+    c = WORKLOADS["c1"]
+    T, B, H = c["T"], c["B"], c["Hkv"]
+    saved = KVCompCacheConfigStatic.config
+    KVCompCacheConfigStatic.config = KVCompCacheConfig("synthetic", QuantMode.ChannelQuant, QuantMode.TokenQuant, c["kblock"], 128,
+                                                      128, 128, c["krel"], c["vrel"])
+    try:
+        cache = KVCompCache(B, H, 128, layers)
+        cos = torch.ones(1, T, 128, dtype=torch.float16, device=device)
+        sin = torch.zeros(1, T, 128, dtype=torch.float16, device=device)
+        for l in range(layers):
+            k, v, _ = make_kv(T, B, H, 128, seed=seed, layer=l, device=device)
+            cache.append(k.permute(1, 2, 0, 3).contiguous(), v.permute(1, 2, 0, 3).contiguous(), l, {"cos": cos, "sin": sin})
+            del k, v
+        k1, v1, q = make_kv(1, B, H, 128, seed=seed + 5, layer=0, device=device)
+        kn, vn, qq = k1.permute(1, 2, 0, 3).contiguous(), v1.permute(1, 2, 0, 3).contiguous(), q.view(B, H, 1, 128)
+        kw = {"cos": cos[:, :1], "sin": sin[:, :1]}
+        scaling = 1.0 / math.sqrt(128)
+
+        def step():
+            for l in range(layers):
+                cache.append(kn, vn, l, kw)
+                cache.attend(qq, l, scaling)
+        for _ in range(4):
+            step()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(steps):
+            step()
+        ev[1].record()
+        torch.cuda.synchronize()
+        cache.check()
+        ms_layer = ev[0].elapsed_time(ev[1]) / steps / layers
+        return {"workload": "KVCompCache.append + attend per layer, c1's shape, %d layers, %d decode steps after a %d-token prefill" % (layers, steps, T),
+                "ms_per_layer": ms_layer, "tokens_per_s_full_model": B / (ms_layer * c["layers"] / 1e3),
+                "recent_window": 128, "includes": "RoPE and transposition of the new token, block compression when the window overflows, fused attention with the window as fp16 tail"}
+    finally:
+        KVCompCacheConfigStatic.config = saved
+        torch.cuda.empty_cache()
 
 
 def recent_window_record(ops, torch, device, seed, layers=4, recent=128):
