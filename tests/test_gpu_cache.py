@@ -486,6 +486,10 @@ def test_rope_store_equals_torch_ops():
         want = apply_rotary_pos_emb_single(x, cos, sin).permute(2, 0, 1, 3).contiguous()
         assert torch.equal(ops.rope_store(x, cos, sin), want)
         assert torch.equal(ops.rope_store(x, cos.expand(B, -1, -1).contiguous(), sin.expand(B, -1, -1).contiguous()), want)
+        # without cos / sin: the transposition alone (new values), into a row range of a larger buffer
+        big = torch.zeros(t + 5, B, H, 128, dtype=torch.float16, device="cuda")
+        ops.rope_store(x, None, None, out=big[3:3 + t])
+        assert torch.equal(big[3:3 + t], x.permute(2, 0, 1, 3)) and not big[:3].any() and not big[3 + t:].any()
 
 
 def test_ctx_stream_room_follows_the_density_seen(cfg):
@@ -518,3 +522,41 @@ def test_ctx_stream_room_follows_the_density_seen(cfg):
     ctx.store(wide[:256])
     assert ctx._enc.buf.numel() - before < 256 * B * H * 128
     assert ctx.compressed_ctx_len == 768
+
+
+@pytest.mark.parametrize("is_k,rec", [(True, 128), (False, 128), (True, 0), (False, 300)])
+def test_rows_behind_the_fused_range_come_from_one_buffer(cfg, is_k, rec):
+    """tail_from(T): the dequantised values of the quantised tokens from T on followed by the recent window,
+    kept in place in one buffer (appends of every size, compressions from the window's front, from a prefill
+    and across both, the buffer's moves to its front, a reader that falls back behind the kept rows and a
+    cache without kept rows)."""
+    from kvcomp_b200.cache import KVCompCtx
+    cfg(kmode="ChannelQuant", krec=rec, vrec=rec, quant_per_sequence=True, wide_min_ints=True)
+    B, H = 2, 2
+    total = 1500
+    k, v, _ = synth(total, B, H, seed=71)
+    x = (k if is_k else v).cuda()
+    rng = np.random.default_rng(5)
+    for keep in (True, False):
+        ctx = KVCompCtx(is_k, B, H, 128, 0.05 if is_k else 0.1, keep_dequantised=keep)
+        n, T = 0, 0
+        sizes = [700] + [int(s) for s in rng.choice([1, 1, 1, 1, 2, 7, 64, 130, 200], size=400)]
+        for step, t in enumerate(sizes):
+            if n + t > total:
+                break
+            ctx.store(x[n:n + t].contiguous())
+            n += t
+            if step % 3 and keep:
+                continue                                  # not every store is followed by a read
+            top = ctx.encoded_ctx_len // 128 * 128
+            if step % 17 == 5:
+                T = max(0, top - 256)                     # a reader that falls back behind what was kept
+            else:
+                T = max(T, top - (128 if step % 2 else 0)) if top else 0
+            T = min(T, top)
+            got = ctx.tail_from(T)
+            want = ctx.get()[0][T:]
+            assert (got is None and want.shape[0] == 0) or torch.equal(got, want), (keep, step, n, T)
+            if got is not None and keep:
+                assert got.data_ptr() % 16 == 0 and got.is_contiguous()
+        assert n > 1200
