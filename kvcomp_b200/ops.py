@@ -16,8 +16,36 @@ MODES = {"BlockQuant": MODE_BLOCK, "ChannelQuant": MODE_CHANNEL, "TokenQuant": M
          "VectorQuant": MODE_VECTOR}
 
 
+# The current device and stream are asked for at every call (a caller may switch either), through the
+# interpreter's direct entries where this torch has them: the public context manager and stream object cost
+# some ten microseconds per call, as much as the rest of a call's host work.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_get_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    if _raw_stream is not None and _get_device is not None:
+        return C.c_void_p(_raw_stream(_get_device()))
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _on:
+    """`with _on(device):` makes the tensor's device current for the call, switching only when it is not."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index if isinstance(device, torch.device) else torch.device(device).index
+
+    def __enter__(self):
+        self.prev = _get_device() if _get_device is not None else torch.cuda.current_device()
+        if self.idx is not None and self.idx != self.prev:
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.idx is not None and self.idx != self.prev:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def _cuda(t, dtype, name):
@@ -106,7 +134,7 @@ def quantize(x, mode, block, rel, batch_shared=True, min_dtype=torch.int8, hist=
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     if hist is not None:
         _cuda(hist, torch.int64, "hist")
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kvc_quantize(_p(x), T, B, H, D, mode, int(batch_shared), block, float(rel), _p(codes),
                                     _p(min_int), min_int.element_size(), _p(scale), _p(hist), _p(ws), ws.numel(),
                                     _p(status), _stream()), "kvc_quantize")
@@ -124,7 +152,7 @@ def quant_minmax(x, mode, block, batch_shared=True):
     mn = torch.empty(n, dtype=torch.float16, device=x.device)
     mx = torch.empty(n, dtype=torch.float16, device=x.device)
     ws = torch.empty(max(8 * n, 16), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _lib.check(lib.kvc_quant_minmax(_p(x), T, B, H, D, mode, int(batch_shared), block, _p(mn), _p(mx), _p(ws),
                                         ws.numel(), _stream()), "kvc_quant_minmax")
     return mn, mx, spec
@@ -150,7 +178,7 @@ def quantize_ranged(x, mode, block, rel, mn, mx, batch_shared=True, min_dtype=to
     ws = torch.empty(max(8 * n, 16), dtype=torch.uint8, device=dev)
     if hist is not None:
         _cuda(hist, torch.int64, "hist")
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kvc_quantize_ranged(_p(x), T, B, H, D, mode, int(batch_shared), block, float(rel), _p(mn), _p(mx),
                                            _p(codes), _p(min_int), min_int.element_size(), _p(scale), _p(hist), _p(ws),
                                            ws.numel(), _p(status), _stream()), "kvc_quantize_ranged")
@@ -173,7 +201,7 @@ def rope_store(x, cos, sin, out=None):
     out = torch.empty((t, B, H, D), dtype=torch.float16, device=x.device) if out is None else _cuda(out, torch.float16, "out")
     if tuple(out.shape) != (t, B, H, D):
         raise KvcError("out must be [t, B, H, D] = %s, got %s" % ((t, B, H, D), tuple(out.shape)))
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _lib.check(lib.kvc_rope_store(_p(x), _p(cos), _p(sin), _p(out), B, H, t, D, stride, _stream()), "kvc_rope_store")
     return out
 
@@ -184,7 +212,7 @@ def dequant(codes, min_int, scale, spec, out=None):
     T, B, H, D = codes.shape
     out = torch.empty((T, B, H, D), dtype=torch.float16, device=codes.device) if out is None else out
     q = spec.qmeta(_cuda(min_int, None, "min_int"), _cuda(scale, torch.float16, "scale"))
-    with torch.cuda.device(codes.device):
+    with _on(codes.device):
         _lib.check(lib.kvc_dequant(_p(codes), C.byref(q), T, B, H, D, _p(out), _stream()), "kvc_dequant")
     return out
 
@@ -194,7 +222,7 @@ def histogram(codes, hist=None):
     lib = _lib.load()
     _cuda(codes, torch.uint8, "codes")
     hist = torch.zeros(256, dtype=torch.int64, device=codes.device) if hist is None else _cuda(hist, torch.int64, "hist")
-    with torch.cuda.device(codes.device):
+    with _on(codes.device):
         _lib.check(lib.kvc_histogram(_p(codes), codes.numel(), _p(hist), _stream()), "kvc_histogram")
     return hist
 
@@ -241,7 +269,7 @@ def build_codebook(hist):
     lib = _lib.load()
     _cuda(hist, torch.int64, "hist")
     blob = torch.empty(BOOK_BYTES, dtype=torch.uint8, device=hist.device)
-    with torch.cuda.device(hist.device):
+    with _on(hist.device):
         _lib.check(lib.kvc_build_codebook(_p(hist), _p(blob), _stream()), "kvc_build_codebook")
     return Book(blob)
 
@@ -250,7 +278,7 @@ def book_from_tree(ref_tree):
     lib = _lib.load()
     _cuda(ref_tree, torch.uint8, "decode_code_book")
     blob = torch.empty(BOOK_BYTES, dtype=torch.uint8, device=ref_tree.device)
-    with torch.cuda.device(ref_tree.device):
+    with _on(ref_tree.device):
         _lib.check(lib.kvc_book_from_tree(_p(ref_tree), ref_tree.numel(), _p(blob), _stream()), "kvc_book_from_tree")
     return Book(blob)
 
@@ -277,7 +305,7 @@ def encode(codes, is_k, enc_table, block_info, thread_info, encoded, base_offset
     if block_info.numel() * block_info.element_size() < nblk * 8 or \
             thread_info.numel() * thread_info.element_size() < nblk * 128:
         raise KvcError("block_infos / thread_infos too small for %d blocks" % nblk)
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kvc_encode(_p(codes), T, cols, int(is_k), _p(enc_table), enc_table.numel() // 8,
                                   int(base_offset), _p(block_info), _p(thread_info), _p(encoded),
                                   encoded.numel(), _p(total), _p(ws), ws.numel(), _p(status), _stream()), "kvc_encode")
@@ -292,7 +320,7 @@ def decode(encoded, block_info, thread_info, book, T, B, H, is_k, out=None, stat
     dev = encoded.device
     out = torch.empty((T, B, H, 128), dtype=torch.uint8, device=dev) if out is None else _cuda(out, torch.uint8, "out")
     status = new_status(dev) if status is None else status
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kvc_decode_bounded(_p(encoded), encoded.numel(), _p(block_info), _p(thread_info), _p(book.blob),
                                           T, B * H, int(is_k), int(max_block), _p(out), _p(status), _stream()), "kvc_decode")
     return out, status
@@ -314,7 +342,7 @@ def fused_qk(cache, T, B, Hkv, q, out=None, out_dtype=torch.float16, status=None
     if out.dtype not in (torch.float16, torch.float32):
         raise KvcError("scores must be fp16 or fp32")
     status = new_status(q.device) if status is None else status
-    with torch.cuda.device(q.device):
+    with _on(q.device):
         _lib.check(lib.kvc_fused_qk(C.byref(cache), T, B, Hkv, Hq, _p(q), _p(out), int(out.dtype == torch.float32),
                                     _p(status), _stream()), "kvc_fused_qk")
     return out, status
@@ -327,7 +355,7 @@ def fused_pv(cache, T, B, Hkv, P, out=None, status=None):
     Hq = P.shape[1]
     out = torch.empty((T // 128, B, Hq, 128), dtype=torch.float16, device=P.device) if out is None else _cuda(out, torch.float16, "C")
     status = new_status(P.device) if status is None else status
-    with torch.cuda.device(P.device):
+    with _on(P.device):
         _lib.check(lib.kvc_fused_pv(C.byref(cache), T, B, Hkv, Hq, _p(P), _p(out), _p(status), _stream()), "kvc_fused_pv")
     return out, status
 
@@ -365,7 +393,7 @@ def attn_decode(kcache, vcache, T, B, Hkv, q, scaling, ktail=None, vtail=None, o
         workspace = attn_workspace(B, Hq, splits if splits > 0 else attn_splits(T, B, Hkv), dev)
     elif workspace is False:        # no workspace at all (splits must be 1): the CTAs take fixed shares of the columns
         workspace = torch.empty(0, dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         _lib.check(lib.kvc_attn_decode(C.byref(kcache) if kcache is not None else None,
                                        C.byref(vcache) if vcache is not None else None, T, B, Hkv, Hq, _p(q), float(scaling),
                                        _p(ktail), _p(vtail), Tr, _p(out), int(splits),
@@ -402,7 +430,7 @@ def attn_decode_static(kcache, vcache, T, B, Hkv, q, scaling, out, ktail=None, v
         Tr = ktail.shape[0]
     else:
         ktail = vtail = None
-    with torch.cuda.device(q.device):
+    with _on(q.device):
         _lib.check(lib.kvc_attn_decode_static(C.byref(kcache), C.byref(vcache), T, B, Hkv, q.shape[1], _p(q),
                                               float(scaling), _p(ktail), _p(vtail), Tr, _p(out), int(splits),
                                               _p(status), _stream()), "kvc_attn_decode_static")
@@ -416,6 +444,6 @@ def k_matvec(k, q, out):
     ctx, bsz, H, D = k.shape
     if bsz != 1 or D != 128:
         raise KvcError("Batch size must be 1 for now")
-    with torch.cuda.device(k.device):
+    with _on(k.device):
         _lib.check(lib.kvc_k_matvec(_p(k), _p(q), _p(out), ctx, H, _stream()), "kvc_k_matvec")
     return out
