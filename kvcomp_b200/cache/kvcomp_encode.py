@@ -311,8 +311,9 @@ class KVCompCtx:
         else:
             kept = None
             if self.keep_dequantised:
-                k = min(n, self.KEEP_ROWS)                    # a long prefill keeps its last rows only
-                xh = ops.dequant(codes, mi, sc, self.spec)[n - k:]
+                k = min(n, max(self.KEEP_ROWS // self.cut_block, 1) * self.cut_block)    # a long prefill keeps its last rows only
+                first = (n - k) // self.spec.tok_div * self.spec.sj                      # unit of the first kept token
+                xh = ops.dequant(codes[n - k:], mi[first:], sc[first:], self.spec)
                 old = self._recent.rows_from_kept(self._recent.kept if k == n else 0)
                 old = None if old is None else old[:self._recent.kept]
                 kept = xh if old is None or not old.shape[0] else torch.cat([old, xh], dim=0)
