@@ -159,6 +159,10 @@ int kvc_quantize_ranged(const void *x, int64_t T, int64_t B, int64_t H, int64_t 
  * alone (how new values reach the token-major recent window).  out may be a row range of a larger buffer. */
 int kvc_rope_store(const void *x, const void *cos_, const void *sin_, void *out, int64_t B, int64_t H, int64_t t,
                    int64_t D, int64_t cos_batch_stride, kvc_stream_t stream);
+/* kvc_rope_store for the new keys (rotated) and for the new values (not rotated) of a decode step in one
+ * launch: k, v device fp16 [B, H, t, D] -> kout, vout device fp16 [t, B, H, D]. */
+int kvc_kv_store(const void *k, const void *v, const void *cos_, const void *sin_, void *kout, void *vout,
+                 int64_t B, int64_t H, int64_t t, int64_t D, int64_t cos_batch_stride, kvc_stream_t stream);
 
 /* (codes + min_int) * scale -> fp16 (models/cache/kvcomp_encode.py:146). */
 int kvc_dequant(const uint8_t *codes, const kvc_qmeta *q, int64_t T, int64_t B, int64_t H, int64_t D,

@@ -62,6 +62,7 @@ _SIGNATURES = {
     "kvc_quantize_ranged": (_i32, [_vp, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _f32, _vp, _vp, _vp, _vp, _i32, _vp,
                                    _vp, _vp, _i64, _vp, _vp]),
     "kvc_rope_store": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "kvc_kv_store": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "kvc_dequant": (_i32, [_vp, C.POINTER(QMeta), _i64, _i64, _i64, _i64, _vp, _vp]),
     "kvc_histogram": (_i32, [_vp, _i64, _vp, _vp]),
     "kvc_build_codebook": (_i32, [_vp, _vp, _vp]),

@@ -74,7 +74,16 @@ class KVCompCache(_BASE):
             self.sins[layer_idx] = safe_cat(self.sins[layer_idx], sin, dim=1)
         elif cfg.enable_quant and key_states.is_cuda and key_states.dtype == torch.float16 and key_states.is_contiguous() \
                 and cos.dtype == torch.float16 and key_states.shape[3] % 16 == 0:
-            kc0 = self._ctx(layer_idx, key_states.shape[1])[0]
+            kc0, vc0 = self._ctx(layer_idx, key_states.shape[1])
+            t = key_states.shape[2]
+            if value_states.is_cuda and value_states.dtype == torch.float16 and value_states.is_contiguous() \
+                    and value_states.shape == key_states.shape:
+                kplace, vplace = kc0.recent_place(t, key_states.device), vc0.recent_place(t, key_states.device)
+                if kplace is not None and vplace is not None:   # the usual decode step: one launch, straight into both windows
+                    ops.kv_store(key_states, value_states, cos, sin, kplace, vplace)
+                    kc0.recent_commit(t)
+                    vc0.recent_commit(t)
+                    return
             place = kc0.recent_place(key_states.shape[2], key_states.device)
             if place is not None:                               # the usual decode step: straight into the recent window
                 ops.rope_store(key_states, cos, sin, out=place)

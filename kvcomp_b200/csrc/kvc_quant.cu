@@ -593,9 +593,12 @@ extern "C" int kvc_k_matvec(const void *k, const void *q, void *out, int64_t ctx
 // models/cache/kvcomp_quant.py:43-48 rotates the new keys (utils/compute.py:25-33: t * cos + rotate_half(t) * sin,
 // every op a rounded fp16 tensor op) before they enter the recent window; the cache keeps tokens token-major.
 // One pass does both: x [B, H, t, D] -> out [t, B, H, D], same bits as torch's four ops and the transposing copy.
+// blockIdx.y = 1 (kvc_kv_store): the same rows of a second tensor xv -> outv without rotation (the new values)
 __global__ void __launch_bounds__(256) rope_store_kernel(const __half *__restrict__ x, const __half *__restrict__ cs,
                                                          const __half *__restrict__ sn, __half *__restrict__ out,
-                                                         long long B, long long H, long long t, int D, long long cs_bstride) {
+                                                         long long B, long long H, long long t, int D, long long cs_bstride,
+                                                         const __half *__restrict__ xv, __half *__restrict__ outv) {
+    if (blockIdx.y == 1) { x = xv; out = outv; cs = nullptr; }
     const int per_row = D / 16;                                  // a thread: 8 channels of the lower half and their partners
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= t * B * H * per_row) return;
@@ -640,7 +643,26 @@ extern "C" int kvc_rope_store(const void *x, const void *cos_, const void *sin_,
     KVC_REQUIRE((n + 255) / 256 < (1ll << 31), "kvc_rope_store: too many elements");
     rope_store_kernel<<<(unsigned)((n + 255) / 256), 256, 0, kvc_cu(stream)>>>(
         reinterpret_cast<const __half *>(x), reinterpret_cast<const __half *>(cos_), reinterpret_cast<const __half *>(sin_),
-        reinterpret_cast<__half *>(out), B, H, t, (int)D, cos_batch_stride);
+        reinterpret_cast<__half *>(out), B, H, t, (int)D, cos_batch_stride, nullptr, nullptr);
+    KVC_LAUNCH_OK();
+    return KVC_OK;
+}
+
+extern "C" int kvc_kv_store(const void *k, const void *v, const void *cos_, const void *sin_, void *kout, void *vout,
+                            int64_t B, int64_t H, int64_t t, int64_t D, int64_t cos_batch_stride, kvc_stream_t stream) {
+    KVC_REQUIRE(k && v && cos_ && sin_ && kout && vout, "kvc_kv_store: null pointer");
+    KVC_REQUIRE(B > 0 && H > 0 && t >= 0 && D > 0 && D % 16 == 0, "kvc_kv_store: bad shape");
+    KVC_REQUIRE(((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(cos_) |
+                  reinterpret_cast<uintptr_t>(sin_) | reinterpret_cast<uintptr_t>(kout) | reinterpret_cast<uintptr_t>(vout)) & 15) == 0,
+                "kvc_kv_store: pointers must be 16-byte aligned");
+    KVC_REQUIRE(cos_batch_stride == 0 || cos_batch_stride == t * D, "kvc_kv_store: cos/sin must be [B, t, D] or [1, t, D]");
+    const long long n = t * B * H * (D / 16);
+    if (n == 0) return KVC_OK;
+    KVC_REQUIRE((n + 255) / 256 < (1ll << 31), "kvc_kv_store: too many elements");
+    rope_store_kernel<<<dim3((unsigned)((n + 255) / 256), 2), 256, 0, kvc_cu(stream)>>>(
+        reinterpret_cast<const __half *>(k), reinterpret_cast<const __half *>(cos_), reinterpret_cast<const __half *>(sin_),
+        reinterpret_cast<__half *>(kout), B, H, t, (int)D, cos_batch_stride,
+        reinterpret_cast<const __half *>(v), reinterpret_cast<__half *>(vout));
     KVC_LAUNCH_OK();
     return KVC_OK;
 }

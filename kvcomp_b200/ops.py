@@ -206,6 +206,25 @@ def rope_store(x, cos, sin, out=None):
     return out
 
 
+def kv_store(k, v, cos, sin, kout, vout):
+    """rope_store for the new keys (rotated) and the new values (not rotated) in one launch: k, v fp16
+    [B, H, t, D] -> kout, vout fp16 [t, B, H, D] (row ranges of the recent windows)."""
+    lib = _lib.load()
+    _cuda(k, torch.float16, "key_states")
+    _cuda(v, torch.float16, "value_states")
+    B, H, t, D = k.shape
+    cos, sin = _cuda(cos.contiguous(), torch.float16, "cos"), _cuda(sin.contiguous(), torch.float16, "sin")
+    if cos.shape != sin.shape or cos.dim() != 3 or cos.shape[1:] != (t, D) or cos.shape[0] not in (1, B):
+        raise KvcError("cos / sin must be [B, t, D] or [1, t, D], got %s" % (tuple(cos.shape),))
+    if tuple(v.shape) != (B, H, t, D) or tuple(kout.shape) != (t, B, H, D) or tuple(vout.shape) != (t, B, H, D):
+        raise KvcError("kv_store: k, v must be [B, H, t, D] and kout, vout [t, B, H, D]")
+    _cuda(kout, torch.float16, "kout")
+    _cuda(vout, torch.float16, "vout")
+    with _on(k.device):
+        _lib.check(lib.kvc_kv_store(_p(k), _p(v), _p(cos), _p(sin), _p(kout), _p(vout), B, H, t, D,
+                                    0 if cos.shape[0] == 1 and B > 1 else t * D, _stream()), "kvc_kv_store")
+
+
 def dequant(codes, min_int, scale, spec, out=None):
     lib = _lib.load()
     _cuda(codes, torch.uint8, "codes")

@@ -490,6 +490,11 @@ def test_rope_store_equals_torch_ops():
         big = torch.zeros(t + 5, B, H, 128, dtype=torch.float16, device="cuda")
         ops.rope_store(x, None, None, out=big[3:3 + t])
         assert torch.equal(big[3:3 + t], x.permute(2, 0, 1, 3)) and not big[:3].any() and not big[3 + t:].any()
+        # keys (rotated) and values (not rotated) in one launch
+        y = (torch.randn(B, H, t, 128, generator=g) * 2).half().cuda()
+        kout, vout = torch.zeros_like(want), torch.zeros_like(want)
+        ops.kv_store(x, y, cos, sin, kout, vout)
+        assert torch.equal(kout, want) and torch.equal(vout, y.permute(2, 0, 1, 3))
 
 
 def test_ctx_stream_room_follows_the_density_seen(cfg):
