@@ -688,6 +688,7 @@ def main():
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling small cases)")
     ap.add_argument("--codec-rels", default="", help="c4: comma-separated error bounds instead of the full sweep (profiling)")
+    ap.add_argument("--side", default="", choices=["", "c1_recent_window"], help="run one side record alone and print it (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="leave out the codec, gpu_reference and strong sub-records")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS, help="device time the repeated timed block has to cover")
@@ -719,6 +720,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     from kvcomp_b200 import ops
+    if args.side == "c1_recent_window":
+        print(json.dumps({"side": args.side, "record": recent_window_record(ops, torch, device, args.seed, layers=args.layers or 4)}), flush=True)
+        return
 
     def barrier():
         torch.cuda.synchronize()

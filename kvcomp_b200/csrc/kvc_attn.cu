@@ -974,17 +974,24 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float *
         const long long b = blockIdx.x / t.Hq, h = (blockIdx.x % t.Hq) / (t.Hq / t.Hkv);
         const long long rstride = (long long)t.B * t.Hkv * 128;                 // halves between two rows of a column
         const __half *kcol = t.ktail + (b * t.Hkv + h) * 128 + part * 64, *vcol = t.vtail + (b * t.Hkv + h) * 128 + ch;
-        if (tid < 128) sm_q[tid] = __half2float(t.q[(size_t)blockIdx.x * 128 + tid]) * t.scaling;
+        // Every load of a pass -- the query (first pass), the thread's half row of K, its 64 rows of V -- is issued
+        // before the first of them is used: one trip to memory per pass instead of one per step of the softmax.
+        const unsigned short qbits = tid < 128 ? ld_nc_16_pinned(t.q + (size_t)blockIdx.x * 128 + tid) : (unsigned short)0;
         for (long long r0 = 0; r0 < t.Tr; r0 += 128) {                        // 128 rows per pass
             const int n_here = (int)min(128ll, t.Tr - r0);
             const bool act = row < n_here;
+            uint4 kv[8];
+            const __half *kr = kcol + (r0 + min(row, n_here - 1)) * rstride;  // rows beyond the pass: read again, not used
+#pragma unroll
+            for (int j = 0; j < 8; j++) kv[j] = ld_nc_128_pinned(kr + j * 8);
+            unsigned short vv[64];
+            const __half *vr = vcol + r0 * rstride;
+#pragma unroll
+            for (int k = 0; k < 64; k++) vv[k] = ld_nc_16_pinned(vr + min(rg * 64 + k, n_here - 1) * rstride);   // rows beyond the pass: weight 0
+            if (r0 == 0 && tid < 128) sm_q[tid] = __half2float(__ushort_as_half(qbits)) * t.scaling;
             __syncthreads();                                                  // sm_q is written; the pass before is done with sm_e
             float sc = -CUDART_INF_F;
             if (act) {
-                const __half *kr = kcol + (r0 + row) * rstride;
-                uint4 kv[8];                                                  // the thread's eight 16-byte loads in flight together
-#pragma unroll
-                for (int j = 0; j < 8; j++) kv[j] = ld_nc_128_pinned(kr + j * 8);
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;                 // four sums: no chain of 64 dependent additions
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
@@ -1017,21 +1024,13 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float *
             for (int w = 0; w < 8; w++) lsum += sm_sum[w];
             l_t = l_t * alpha + lsum;
             m_t = m_new;
-            // rows rg * 64 .. + 63 of the pass, 32 loads in flight at a time, four sums
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-            const __half *vr = vcol + r0 * rstride;
-#pragma unroll 1
-            for (int i0 = rg * 64; i0 < min(n_here, rg * 64 + 64); i0 += 32) {
-                unsigned short vv[32];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;                     // rows rg * 64 .. + 63 of the pass, four sums
 #pragma unroll
-                for (int k = 0; k < 32; k++) vv[k] = ld_nc_16_pinned(vr + min(i0 + k, n_here - 1) * rstride);   // rows beyond the pass: weight 0
-#pragma unroll
-                for (int k = 0; k < 32; k += 4) {
-                    d0 = fmaf(sm_e[min(i0 + k, 127)], __half2float(__ushort_as_half(vv[k])), d0);
-                    d1 = fmaf(sm_e[min(i0 + k + 1, 127)], __half2float(__ushort_as_half(vv[k + 1])), d1);
-                    d2 = fmaf(sm_e[min(i0 + k + 2, 127)], __half2float(__ushort_as_half(vv[k + 2])), d2);
-                    d3 = fmaf(sm_e[min(i0 + k + 3, 127)], __half2float(__ushort_as_half(vv[k + 3])), d3);
-                }
+            for (int k = 0; k < 64; k += 4) {
+                d0 = fmaf(sm_e[rg * 64 + k], __half2float(__ushort_as_half(vv[k])), d0);
+                d1 = fmaf(sm_e[rg * 64 + k + 1], __half2float(__ushort_as_half(vv[k + 1])), d1);
+                d2 = fmaf(sm_e[rg * 64 + k + 2], __half2float(__ushort_as_half(vv[k + 2])), d2);
+                d3 = fmaf(sm_e[rg * 64 + k + 3], __half2float(__ushort_as_half(vv[k + 3])), d3);
             }
             o_t = fmaf(o_t, alpha, (d0 + d1) + (d2 + d3));
         }
