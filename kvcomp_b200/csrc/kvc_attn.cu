@@ -1204,9 +1204,6 @@ constexpr int ATTN_ITEMS_PER_CTA = 4;
 // end of every column short runs of half that, enough of them that each resident CTA finds about two
 // short items to finish with.  The short items are handed out last (the item order puts them behind
 // all long ones), so the CTAs of a launch end within one short item of each other.
-#ifndef KVC_EXP_SHORT
-#define KVC_EXP_SHORT 4
-#endif
 struct RunPlan { int tps, long_runs, short_tiles, splits; };
 static RunPlan plan_runs(long long n_tiles, long long cols, int sm_count) {
     RunPlan r = {1, 1, 1, 1};
@@ -1216,7 +1213,7 @@ static RunPlan plan_runs(long long n_tiles, long long cols, int sm_count) {
     if (tps < 1) tps = 1;
     if (tps > n_tiles) tps = n_tiles;
     // (items of a single tile pay the per-item work too often: measured slower than no short runs at all)
-    long long short_tiles = tps >= KVC_EXP_SHORT ? tps / 2 : tps;
+    long long short_tiles = tps >= 4 ? tps / 2 : tps;
     long long short_region = 0;                                      // tiles of a column cut into short runs
     if (short_tiles < tps) {
         short_region = (2 * P * short_tiles + cols - 1) / cols;       // about two short items per CTA over all columns
