@@ -136,3 +136,63 @@ def test_attention_run_plan_without_a_gpu():
     assert lib.kvc_attn_splits(4096, 8, 32, sms) == 8          # runs of 2 tiles
     assert lib.kvc_attn_splits(32768, 16, 8, sms) == 20        # 10 runs of 9 tiles, then 10 of (at most) 4
     assert lib.kvc_attn_splits(0, 8, 32, sms) == 1
+
+
+def test_recent_rows_buffer_against_a_list_model():
+    """The in-place buffer of the cache's rows behind the stream ([kept dequantised rows | recent window]) does
+    what a plain list of rows would: appends of every size, rows produced in place, fronts consumed into the kept
+    part, kept rows given up, moves to the front and growth of the buffer, rebuilds."""
+    import torch
+    from kvcomp_b200.cache.kvcomp_encode import _RecentRows
+    rng = np.random.default_rng(3)
+    rr, kept, recent, nxt = _RecentRows(), [], [], 0
+    shape = (2, 1, 4)
+
+    def rows(n):
+        nonlocal nxt
+        t = torch.arange(nxt, nxt + n, dtype=torch.float32).view(n, 1, 1, 1).expand(n, *shape).contiguous()
+        nxt += n
+        return t
+
+    def check():
+        assert len(rr) == len(recent) and rr.kept == len(kept)
+        got = rr.rows_from_kept(len(kept))
+        want = kept + recent
+        if not want:
+            assert got is None
+        else:
+            assert got.is_contiguous() and [int(v) for v in got[:, 0, 0, 0]] == want
+            assert [int(v) for v in rr.view()[:, 0, 0, 0]] == recent
+    moves = 0
+    for step in range(3000):
+        op = rng.integers(0, 6)
+        before = None if rr.buf is None else rr.buf.data_ptr()
+        if op <= 1:                                   # append
+            n = int(rng.choice([1, 1, 1, 2, 5, 40]))
+            r = rows(n)
+            rr.append(r, room=8)
+            recent += [int(v) for v in r[:, 0, 0, 0]]
+        elif op == 2:                                 # rows produced in place
+            n = int(rng.integers(1, 4))
+            place = rr.reserve(n, 8, shape, torch.float32, torch.device("cpu"))
+            r = rows(n)
+            place.copy_(r)
+            rr.commit(n)
+            recent += [int(v) for v in r[:, 0, 0, 0]]
+        elif op == 3 and recent:                      # the window's front is compressed and kept as dequantised rows
+            n = int(rng.integers(1, len(recent) + 1))
+            rr.view()[:n] += 100000                   # "dequantised in place"
+            rr.consume(n)
+            kept += [v + 100000 for v in recent[:n]]
+            recent = recent[n:]
+        elif op == 4 and kept:                        # a reader has moved on
+            k = int(rng.integers(0, len(kept) + 1))
+            rr.rows_from_kept(k)
+            kept = kept[len(kept) - k:]
+        elif op == 5 and step % 7 == 0:               # start over (a prefill, a read from a file)
+            k, r = rows(int(rng.integers(0, 4))), rows(int(rng.integers(0, 6)))
+            rr.rebuild(k if k.shape[0] else None, r if r.shape[0] else None, room=8)
+            kept, recent = [int(v) for v in k[:, 0, 0, 0]], [int(v) for v in r[:, 0, 0, 0]]
+        moves += before is not None and rr.buf is not None and rr.buf.data_ptr() != before
+        check()
+    assert nxt > 3000 and moves < 400                 # the buffer is replaced now and then, not at every step
