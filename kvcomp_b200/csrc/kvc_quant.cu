@@ -598,6 +598,9 @@ __global__ void __launch_bounds__(256) rope_store_kernel(const __half *__restric
                                                          const __half *__restrict__ sn, __half *__restrict__ out,
                                                          long long B, long long H, long long t, int D, long long cs_bstride,
                                                          const __half *__restrict__ xv, __half *__restrict__ outv) {
+    // A kernel launched behind this one with programmatic stream serialisation (the fused attention) may set up
+    // while these few rows are written: it touches them only after its own grid-dependency wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (blockIdx.y == 1) { x = xv; out = outv; cs = nullptr; }
     const int per_row = D / 16;                                  // a thread: 8 channels of the lower half and their partners
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
