@@ -19,11 +19,14 @@ Prints ONE JSON line (rank 0).  Besides the headline it carries
                  tensor at five error bounds: encode / decode GB/s, compression ratio, bits per symbol
   gpu_reference  (N = 1, when baseline/_ref/kvcomp_cuda.so is present) the reference's own fused K and
                  V kernels timed beside this library's on the reference's own shapes
-  other_workloads (N = 1) the two grouped-query configurations, a few layers each: per-layer time and roofline fraction
+  other_workloads (N = 1) the two grouped-query configurations, a few layers each: per-layer time and roofline
+                 fraction; c1 with its newest 128 tokens as the uncompressed recent window; a decode loop
+                 through the cache class the model files call (append + attend per layer)
   strong         (N > 1) the Mistral-shaped GQA cache with its KV heads split over the ranks and one NCCL
                  all-gather of the outputs per step, against the same layers on one GPU
   cpu_baseline   (N = 1) the CPU restatement of the reference's path on a bounded sample
 --impl reference times that CPU restatement (oracle/, OpenMP over the host cores) instead.
+Profiling helpers: --layers, --no-extras, --min-seconds, --codec-rels (c4: fewer error bounds), --side (one side record alone).
 """
 import argparse
 import importlib.util
